@@ -3,10 +3,11 @@ from .engine_config import EngineConfig
 from .errors import ConfigError
 from .bidonex import BidonexConfig
 from .qwen2 import Qwen2Config
+from .pukerax import PukeraxConfig
 from .zugarax import ZugaraxConfig
 from .registry import ARCHITECTURES, Architecture, register_architecture, resolve, resolve_folder
 
 __all__ = [
     "ARCHITECTURES", "Architecture", "BidonexConfig", "ConfigError", "EngineConfig", "LayerSpec", "ModelSpec", "PartSpec", "Qwen2Config",
-    "ScheduleEntry", "ZugaraxConfig", "register_architecture", "resolve", "resolve_folder",
+    "PukeraxConfig", "ScheduleEntry", "ZugaraxConfig", "register_architecture", "resolve", "resolve_folder",
 ]

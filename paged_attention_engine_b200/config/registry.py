@@ -18,6 +18,7 @@ from .errors import ConfigError
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .bidonex import BidonexConfig
 from .qwen2 import Qwen2Config
+from .pukerax import PukeraxConfig
 from .zugarax import ZugaraxConfig
 
 
@@ -274,3 +275,97 @@ def zugarax_spec(cfg: ZugaraxConfig) -> ModelSpec:
 
 
 register_architecture("Zugarax", ZugaraxConfig, zugarax_spec)
+
+
+# --------------------------------------------------------------------------- #
+# Pukerax: a token embedding into float32; S residual streams joined by hyper-connections (each
+# sublayer reads a weighted sum of the streams and its output is written back into all of them
+# while a small matrix mixes them), or one stream with plain sums; RMS norms whose weights are
+# stored around zero; latent attention whose queries go through a normed latent of their own and
+# whose heads are gated by one sigmoid each; a feed-forward of squared ReLUs, dense or routed
+# (softmax scores, a correction added for the choice only, groups of experts, experts that return
+# their input, a shared expert); the streams' sum, RMS norm and an untied head at the end.
+# --------------------------------------------------------------------------- #
+
+# The design has no longest sequence; positions are 32-bit integers.
+PUKERAX_MAX_POSITIONS = 1 << 30
+# Fixed by the design: what is added to the sum of the chosen experts' scores before the division.
+PUKERAX_WEIGHT_EPS = 1e-20
+
+
+def pukerax_spec(cfg: PukeraxConfig) -> ModelSpec:
+    layers = []
+    streams = cfg.streams
+    for i, layer in enumerate(cfg.layers):
+        prefix = f"l{i}"
+        m = layer.mixer
+        mixer = PartSpec(
+            "latent_attention",
+            {
+                "hidden_size": cfg.width, "num_heads": m.heads, "head_dim": m.dim, "rot_dim": m.rot_dim,
+                "value_dim": m.vdim, "kv_rank": m.kv_rank, "q_rank": m.q_rank, "scale": m.scale, "norm_eps": cfg.norm_eps,
+                "head_gate": True,
+                "position_encoding": {"kind": "scaled_rotary", "dims": m.rot_dims, "base": m.rot_base, "scaling": None},
+            },
+            f"{prefix}.mix",
+        )
+        feed_forward = None
+        if layer.mlp is not None and layer.mlp.kind == "dense":
+            feed_forward = PartSpec(
+                "dense_mlp", {"hidden_size": cfg.width, "intermediate_size": layer.mlp.ff, "activation": "relu2"},
+                names={"up.weight": f"{prefix}.mlp.up", "down.weight": f"{prefix}.mlp.down"})
+        elif layer.mlp is not None:
+            r = layer.mlp.router
+            feed_forward = PartSpec(
+                "routed_experts",
+                {
+                    "hidden_size": cfg.width, "intermediate_size": layer.mlp.ff, "activation": "relu2",
+                    "num_experts": r.experts, "identity_experts": r.identity, "top": r.top, "score": "softmax",
+                    "choice_correction": True, "group_count": r.group_count, "group_keep": r.group_keep,
+                    "weight_eps": PUKERAX_WEIGHT_EPS, "weight_scale": r.scale, "shared_size": layer.mlp.shared_ff,
+                },
+                f"{prefix}.mlp",
+            )
+
+        def norm(name, q):
+            if streams:
+                return PartSpec("stream_rms_norm", {"size": cfg.width, "streams": streams, "eps": cfg.norm_eps, "weight_offset": 1.0,
+                                                    "weighted_read": True},
+                                names={"weight": f"{prefix}.{name}", "read": f"{prefix}.hc{q}.in"})
+            return PartSpec("rms_norm", {"size": cfg.width, "eps": cfg.norm_eps, "out": "engine", "weight_offset": 1.0},
+                            names={"weight": f"{prefix}.{name}"})
+
+        parts = dict(mixer_norm=norm("norm1", 1), mixer=mixer)
+        if feed_forward is not None:
+            parts.update(feed_forward_norm=norm("norm2", 2), feed_forward=feed_forward)
+        if streams:
+            parts["mixer_merge"] = PartSpec("hyper_connection", {"streams": streams}, f"{prefix}.hc1")
+            if feed_forward is not None:
+                parts["feed_forward_merge"] = PartSpec("hyper_connection", {"streams": streams}, f"{prefix}.hc2")
+            block = "hyper_connected" if feed_forward is not None else "hyper_connected_mixer"
+        else:
+            block = "pre_norm_residual" if feed_forward is not None else "mixer_residual"
+            if feed_forward is None:
+                parts = dict(norm=parts["mixer_norm"], mixer=mixer)
+        layers.append(LayerSpec(block, parts))
+    if streams:
+        final_norm = PartSpec("stream_rms_norm", {"size": cfg.width, "streams": streams, "eps": cfg.norm_eps, "weight_offset": 1.0,
+                                                  "weighted_read": False}, names={"weight": "final.norm"})
+    else:
+        final_norm = PartSpec("rms_norm", {"size": cfg.width, "eps": cfg.norm_eps, "out": "engine", "weight_offset": 1.0},
+                              names={"weight": "final.norm"})
+    return ModelSpec(
+        architecture=cfg.architecture,
+        vocab_size=cfg.vocab,
+        hidden_size=cfg.width,
+        max_positions=PUKERAX_MAX_POSITIONS,
+        embedding=PartSpec("scaled_token_embedding", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "scale": 1.0},
+                           names={"weight": "embed"}),
+        layers=tuple(layers),
+        schedule=tuple(ScheduleEntry(i) for i in range(len(cfg.layers))),
+        final_norm=final_norm,
+        head=PartSpec("lm_head", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "tied_to": None}, names={"weight": "head"}),
+    )
+
+
+register_architecture("Pukerax", PukeraxConfig, pukerax_spec)

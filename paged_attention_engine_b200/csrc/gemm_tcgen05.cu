@@ -50,7 +50,7 @@ struct Params {
   int ld_out;        // NORMAL: row pitch of out/residual in elements; SWAPPED: weight rows N
   int out_f32;
   int swiglu;        // NORMAL only: columns come in blocks of 16 gate, 16 up; out[row, n / 2] = silu(gate) * up
-  int activation;    // 0: none; 1: exact GELU, 2: tanh GELU, of the product (+ bias) rounded to the output's type, before the residual
+  int activation;    // 0: none; 1: exact GELU, 2: tanh GELU, 3: squared ReLU, of the product (+ bias) rounded to the output's type, before the residual
   // q|k|v with rotation and page write in the epilogue (NORMAL, many tokens): out is
   // qkv [tokens, (heads + 2 kv_heads) d]; a tile of 256 columns holds whole heads.
   int rotary;
@@ -83,6 +83,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ float activation_of(float z, int kind, bool out_f32) {
   if (!out_f32) z = __bfloat162float(__float2bfloat16_rn(z));
   if (kind == 1) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+  if (kind == 3) { z = fmaxf(z, 0.f); return z * z; }
   return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
 }
 
@@ -824,7 +825,7 @@ PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const
                                   int tokens, int n, int k, int out_f32, int activation, int* error, void* stream) {
   if (tokens == 0 || n == 0) return 0;
   if (int err = check_operands(x, w, k)) return err;
-  if (activation < 0 || activation > 2) return fail(2, "linear_tcgen05: activation %d (0: none, 1: exact GELU, 2: tanh GELU)", activation);
+  if (activation < 0 || activation > 3) return fail(2, "linear_tcgen05: activation %d (0: none, 1: exact GELU, 2: tanh GELU, 3: squared ReLU)", activation);
   Params p{};
   p.activation = activation;
   p.out = out;

@@ -115,16 +115,17 @@ __global__ void rotary_table_amplitude_kernel(float* __restrict__ table, const i
   table[(size_t)t * 2 * half + half + f] = s * amplitude;
 }
 
-// out[t, c] = x[t, c] * sigmoid(gate[t, gate_off + c]); the gate is a column range of a projection.
+// out[t, c] = x[t, c] * sigmoid(gate[t, gate_off + c / group]); the gate is a column range of a
+// projection, one column for every `group` neighbouring channels (a head's size: a gate per head).
 template <typename TX, typename TG>
 __global__ void sigmoid_gate_kernel(TX* __restrict__ out, const TX* __restrict__ x, const TG* __restrict__ gate,
-                                    long long total, int width, int gate_ld, int gate_off) {
+                                    long long total, int width, int gate_ld, int gate_off, int group) {
   dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long t = i / width;
   const int c = (int)(i - t * width);
-  const float g = to_float(gate[t * gate_ld + gate_off + c]);
+  const float g = to_float(gate[t * gate_ld + gate_off + c / group]);
   out[i] = from_float<TX>(to_float(x[i]) / (1.f + expf(-g)));
 }
 
@@ -172,19 +173,20 @@ PAE_EXPORT int pae_rotary_table_amplitude(float* table, const int* positions, co
   return check_launch("rotary_table_amplitude");
 }
 
-// x, out [tokens, width] in x_dtype; gate [tokens, gate_ld] in gate_dtype, columns gate_off .. gate_off + width.
+// x, out [tokens, width] in x_dtype; gate [tokens, gate_ld] in gate_dtype, columns gate_off .. gate_off + width / group.
 PAE_EXPORT int pae_sigmoid_gate(void* out, const void* x, const void* gate, int tokens, int width, int gate_ld,
-                                int gate_off, int x_dtype, int gate_dtype, void* stream) {
+                                int gate_off, int group, int x_dtype, int gate_dtype, void* stream) {
   const long long total = (long long)tokens * width;
   if (total == 0) return 0;
-  if (gate_off < 0 || gate_off + width > gate_ld) return fail(2, "sigmoid_gate: columns %d..%d of rows of %d", gate_off, gate_off + width, gate_ld);
+  if (group < 1 || width % group) return fail(2, "sigmoid_gate: rows of %d channels in groups of %d", width, group);
+  if (gate_off < 0 || gate_off + width / group > gate_ld) return fail(2, "sigmoid_gate: columns %d..%d of rows of %d", gate_off, gate_off + width / group, gate_ld);
   cudaStream_t s = (cudaStream_t)stream;
   using bf = __nv_bfloat16;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   const int key = x_dtype * 10 + gate_dtype;
-  if (key == 0) launch_kernel(sigmoid_gate_kernel<float, float>, blocks, 256, 0, s, (float*)out, (const float*)x, (const float*)gate, total, width, gate_ld, gate_off);
-  else if (key == 10) launch_kernel(sigmoid_gate_kernel<bf, float>, blocks, 256, 0, s, (bf*)out, (const bf*)x, (const float*)gate, total, width, gate_ld, gate_off);
-  else if (key == 11) launch_kernel(sigmoid_gate_kernel<bf, bf>, blocks, 256, 0, s, (bf*)out, (const bf*)x, (const bf*)gate, total, width, gate_ld, gate_off);
+  if (key == 0) launch_kernel(sigmoid_gate_kernel<float, float>, blocks, 256, 0, s, (float*)out, (const float*)x, (const float*)gate, total, width, gate_ld, gate_off, group);
+  else if (key == 10) launch_kernel(sigmoid_gate_kernel<bf, float>, blocks, 256, 0, s, (bf*)out, (const bf*)x, (const float*)gate, total, width, gate_ld, gate_off, group);
+  else if (key == 11) launch_kernel(sigmoid_gate_kernel<bf, bf>, blocks, 256, 0, s, (bf*)out, (const bf*)x, (const bf*)gate, total, width, gate_ld, gate_off, group);
   else return fail(1, "sigmoid_gate: element types x=%d gate=%d are not supported", x_dtype, gate_dtype);
   return check_launch("sigmoid_gate");
 }

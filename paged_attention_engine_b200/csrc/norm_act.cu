@@ -53,10 +53,10 @@ __global__ void embedding_positions_kernel(float* __restrict__ out, const T* __r
 // sum of squares is double, the rest float32, one rounding at the end.
 template <typename TI, typename TO>
 __global__ void rms_norm_cast_kernel(TO* __restrict__ out, const TI* __restrict__ x, const float* __restrict__ weight,
-                                     int width, float eps) {
+                                     int width, float eps, int ld) {
   dependent_launch_prologue();
   __shared__ double scratch[32];
-  const TI* row = x + (size_t)blockIdx.x * width;
+  const TI* row = x + (size_t)blockIdx.x * ld;       // a row of x may be a column range of a wider row
   double squares = 0.0;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const double v = (double)to_float(row[i]);
@@ -141,10 +141,11 @@ __global__ void layer_norm_kernel(TO* __restrict__ out, const TI* __restrict__ x
 
 __device__ __forceinline__ float gelu_of(float z, int kind) {
   if (kind == 0) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+  if (kind == 2) { z = fmaxf(z, 0.f); return z * z; }
   return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
 }
 
-// kind 0: 0.5 z (1 + erf(z / sqrt 2)); kind 1: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// kind 0: 0.5 z (1 + erf(z / sqrt 2)); kind 1: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); kind 2: max(z, 0)^2.
 template <typename T>
 __global__ void gelu_kernel(T* __restrict__ out, const T* __restrict__ x, long long total, int kind) {
   dependent_launch_prologue();
@@ -285,16 +286,32 @@ PAE_EXPORT int pae_rms_norm_cast(void* out, const void* x, const float* weight, 
   using bf = __nv_bfloat16;
   const int key = in_dtype * 10 + out_dtype;
   if (key == 0)
-    launch_kernel(rms_norm_cast_kernel<float, float>, rows, threads, 0, s, (float*)out, (const float*)x, weight, width, eps);
+    launch_kernel(rms_norm_cast_kernel<float, float>, rows, threads, 0, s, (float*)out, (const float*)x, weight, width, eps, width);
   else if (key == 1)
-    launch_kernel(rms_norm_cast_kernel<float, bf>, rows, threads, 0, s, (bf*)out, (const float*)x, weight, width, eps);
+    launch_kernel(rms_norm_cast_kernel<float, bf>, rows, threads, 0, s, (bf*)out, (const float*)x, weight, width, eps, width);
   else if (key == 10)
-    launch_kernel(rms_norm_cast_kernel<bf, float>, rows, threads, 0, s, (float*)out, (const bf*)x, weight, width, eps);
+    launch_kernel(rms_norm_cast_kernel<bf, float>, rows, threads, 0, s, (float*)out, (const bf*)x, weight, width, eps, width);
   else if (key == 11)
-    launch_kernel(rms_norm_cast_kernel<bf, bf>, rows, threads, 0, s, (bf*)out, (const bf*)x, weight, width, eps);
+    launch_kernel(rms_norm_cast_kernel<bf, bf>, rows, threads, 0, s, (bf*)out, (const bf*)x, weight, width, eps, width);
   else
     return fail(1, "rms_norm_cast: element types in=%d out=%d are not supported", in_dtype, out_dtype);
   return check_launch("rms_norm_cast");
+}
+
+// The same norm over columns [offset, offset + width) of float32 rows of pitch ld -> out [rows, width].
+PAE_EXPORT int pae_rms_norm_columns(void* out, const float* x, int ld, int offset, const float* weight, int rows, int width,
+                                    float eps, int out_dtype, void* stream) {
+  if (rows == 0 || width == 0) return 0;
+  if (offset < 0 || offset + width > ld) return fail(2, "rms_norm_columns: columns %d..%d of rows of %d", offset, offset + width, ld);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = row_threads(width);
+  if (out_dtype == kF32)
+    launch_kernel(rms_norm_cast_kernel<float, float>, rows, threads, 0, s, (float*)out, x + offset, weight, width, eps, ld);
+  else if (out_dtype == kBF16)
+    launch_kernel(rms_norm_cast_kernel<float, __nv_bfloat16>, rows, threads, 0, s, (__nv_bfloat16*)out, x + offset, weight, width, eps, ld);
+  else
+    return fail(1, "rms_norm_columns: unknown dtype %d", out_dtype);
+  return check_launch("rms_norm_columns");
 }
 
 // gate_up [tokens, 2 * inter] in in_dtype -> out [tokens, inter] in out_dtype.
@@ -335,7 +352,7 @@ PAE_EXPORT int pae_softcap(float* x, long long total, float cap, void* stream) {
 
 PAE_EXPORT int pae_gelu(void* out, const void* x, long long total, int kind, int dtype, void* stream) {
   if (total == 0) return 0;
-  if (kind != 0 && kind != 1) return fail(2, "gelu: kind %d (0: erf, 1: tanh)", kind);
+  if (kind < 0 || kind > 2) return fail(2, "gelu: kind %d (0: erf, 1: tanh, 2: squared ReLU)", kind);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kBF16 && total % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
     const long long chunks = total / 8;

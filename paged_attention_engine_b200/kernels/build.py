@@ -54,6 +54,8 @@ FAMILIES: dict[str, list[str]] = {
     "head_prep": ["head_prep.cu", "common.cuh"],
     "matrix_memory": ["matrix_memory.cu", "common.cuh"],
     "linear_heads": ["linear_heads.cu", "attention_mma.cuh", "common.cuh"],
+    "streams": ["streams.cu", "common.cuh"],
+    "routing": ["routing.cu", "common.cuh"],
     "attention_decode_noalloc": [
         "attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_mma.cuh", "common.cuh",
     ],

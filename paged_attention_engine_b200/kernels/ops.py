@@ -206,11 +206,34 @@ class PendingNorm:
         return self.x.device
 
 
+class PendingStreams:
+    """Residual streams [tokens, streams * width] whose write x'_t = sum_s mix[s, t] x_s + out[t] y has
+    not run: `streams_write` returns one, and the `streams_read_norm` of the next sublayer does
+    the write inside its own kernel; anything else calls `materialized`, which runs the write alone."""
+
+    def __init__(self, x, y, mix, out_w, streams: int) -> None:
+        self.x, self.y, self.mix, self.out_w, self.streams = x, y, mix, out_w, streams
+        self.dtype = torch.float32
+        self.value = None
+
+    @property
+    def shape(self):
+        return (self.x.shape[0], self.streams * self.y.shape[-1])
+
+    @property
+    def device(self):
+        return self.x.device
+
+
 def materialized(x):
-    """The tensor that `x` stands for (x itself unless it is a PendingSum or a PendingNorm)."""
+    """The tensor that `x` stands for (x itself unless it is a PendingSum, a PendingNorm or PendingStreams)."""
     if isinstance(x, PendingNorm):
         if x.value is None:
             x.value = _rms_norm_now(x.x, x.weight, x.eps)
+        return x.value
+    if isinstance(x, PendingStreams):
+        if x.value is None:
+            _streams_step(x, None, None, 0.0, None)
         return x.value
     if not isinstance(x, PendingSum):
         return x
@@ -414,16 +437,16 @@ def _tensor_core_shape(x, weight, residual, out_dtype) -> bool:
     )
 
 
-ACTIVATIONS = {None: 0, "gelu_erf": 1, "gelu_tanh": 2}
+ACTIVATIONS = {None: 0, "gelu_erf": 1, "gelu_tanh": 2, "relu2": 3}
 
 
 def linear(x, weight, bias=None, residual=None, out_dtype=None, activation: str | None = None) -> torch.Tensor:
     """x [M, K] . weight [N, K]^T (+ bias [N], float32) (+ residual [M, N]) -> [M, N]. `activation`
-    ("gelu_erf", "gelu_tanh") is applied to the product (+ bias), rounded to the output's dtype first,
+    ("gelu_erf", "gelu_tanh", "relu2": the square of max(z, 0)) is applied to the product (+ bias), rounded to the output's dtype first,
     before the residual: in the tensor-core product's epilogue or in the sum of its splits, else
     by the activation's own kernel."""
     if activation not in ACTIVATIONS:
-        raise KernelError(f"linear: activation '{activation}' (known: gelu_erf, gelu_tanh)")
+        raise KernelError(f"linear: activation '{activation}' (known: gelu_erf, gelu_tanh, relu2)")
     if (activation is None and bias is None and out_dtype in (None, torch.bfloat16) and weight.dtype == torch.bfloat16 and weight.dim() == 2
             and weight.data_ptr() % 16 == 0 and weight.shape[0] <= 65536):
         source, norm_weight, eps = _norm_of(x)
@@ -906,6 +929,21 @@ def rms_norm_cast(x, weight: torch.Tensor, eps: float, out_dtype=None) -> torch.
     return out
 
 
+def rms_norm_columns(x, offset: int, width: int, weight: torch.Tensor, eps: float, out_dtype) -> torch.Tensor:
+    """The RMS norm, times `weight`, of columns [offset, offset + width) of float32 rows, in `out_dtype`
+    [rows, width]: a part of a fused projection that is normed on its own (a latent)."""
+    x = materialized(x)
+    _need(x, "rms_norm_columns: x", torch.float32)
+    _need(weight, "rms_norm_columns: weight", torch.float32)
+    if weight.numel() != width:
+        raise KernelError(f"rms_norm_columns: weight of {weight.numel()} for {width} columns")
+    out = torch.empty((x.shape[0], width), dtype=out_dtype, device=x.device)
+    lib = _lib("norm_act")
+    _check(lib, lib.pae_rms_norm_columns(_ptr(out), _ptr(x), x.shape[1], offset, _ptr(weight), x.shape[0], width, float(eps),
+                                         _DTYPE_CODE[out_dtype], _stream()))
+    return out
+
+
 def clamped_glu(gate_up, limit: float, alpha: float, out_dtype=None) -> torch.Tensor:
     """g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), for
     rows [tokens, 2 I] that hold the gate in columns [0, I) and the up projection in [I, 2 I)."""
@@ -983,8 +1021,9 @@ def head_prep(proj, *, q_off: int, k_off: int, v_off: int, heads: int, kv_heads:
     return q
 
 
-def sigmoid_gate(x, gate_proj, gate_off: int) -> torch.Tensor:
-    """x * sigmoid(gate_proj[:, gate_off : gate_off + x.shape[1]])."""
+def sigmoid_gate(x, gate_proj, gate_off: int, group: int = 1) -> torch.Tensor:
+    """x * sigmoid(gate_proj[:, gate_off : gate_off + x.shape[1] / group]): a gate column for every
+    `group` neighbouring channels of x (1: a gate per channel; a head's size: a gate per head)."""
     x = materialized(x)
     gate_proj = materialized(gate_proj)
     _need(x, "sigmoid_gate: x")
@@ -993,8 +1032,10 @@ def sigmoid_gate(x, gate_proj, gate_off: int) -> torch.Tensor:
         raise KernelError(f"sigmoid_gate: {x.shape[0]} rows and {gate_proj.shape[0]} rows of gates")
     out = torch.empty_like(x)
     lib = _lib("head_prep")
+    if group < 1 or x.shape[1] % group:
+        raise KernelError(f"sigmoid_gate: rows of {x.shape[1]} channels do not split into groups of {group}")
     _check(lib, lib.pae_sigmoid_gate(_ptr(out), _ptr(x), _ptr(gate_proj), x.shape[0], x.shape[1], gate_proj.shape[1], gate_off,
-                                     _code(x), _code(gate_proj), _stream()))
+                                     group, _code(x), _code(gate_proj), _stream()))
     return out
 
 
@@ -1077,7 +1118,7 @@ def layer_norm(x, weight: torch.Tensor, bias: torch.Tensor | None, eps: float, o
     return out
 
 
-GELU_KINDS = {"gelu_erf": 0, "gelu_tanh": 1}
+GELU_KINDS = {"gelu_erf": 0, "gelu_tanh": 1, "relu2": 2}
 
 
 def gelu(x, kind: str = "gelu_erf") -> torch.Tensor:
@@ -1278,4 +1319,125 @@ def delta_rule(proj, offsets, w_pre, w0, a_bias, gate_offset, norm_weight, state
     out = torch.empty((tokens, width), dtype=out_dtype, device=proj.device)
     _check(lib, lib.pae_delta_rule_output(_ptr(out), _ptr(o), proj.data_ptr() + 4 * gate_offset, ld, _ptr(norm_weight), tokens,
                                           num_heads, head_dim, norm_eps, _DTYPE_CODE[out_dtype], _stream()))
+    return out
+
+
+# ----------------------------------------------------------------------------------- #
+# Hyper-connections (csrc/streams.cu) and routed experts (csrc/routing.cu)
+
+def _sublayer_output(y):
+    """(float32 planes [splits, tokens, width], splits) of a sublayer's output that is a tensor or a
+    split product without bias, residual or activation."""
+    if isinstance(y, PendingSum) and y.value is None and y.bias is None and y.residual is None and not y.activation and fuse_split_sums:
+        return y.partial, int(y.partial.shape[0])
+    y = materialized(y)
+    _need(y, "streams: the sublayer's output", torch.float32)
+    return y, 1
+
+
+def _streams_launch(x, src_streams: int, streams: int, width: int, y, splits: int, mix, out_w, in_w, norm_w, eps: float, out_dtype):
+    tokens = x.shape[0]
+    x_new = torch.empty((tokens, streams * width), dtype=torch.float32, device=x.device) if y is not None else None
+    normed = torch.empty((tokens, width), dtype=out_dtype, device=x.device) if norm_w is not None else None
+    lib = _lib("streams")
+    _check(lib, lib.pae_streams_step(_ptr(x_new), _ptr(normed), _ptr(x), src_streams, _ptr(y), splits, _ptr(mix), _ptr(out_w),
+                                     _ptr(in_w), _ptr(norm_w), tokens, streams, width, float(eps),
+                                     _DTYPE_CODE[out_dtype] if out_dtype is not None else 0, _stream()))
+    return x_new, normed
+
+
+def _streams_step(pending, in_w, norm_w, eps: float, out_dtype):
+    """Runs the write of a PendingStreams and, with a norm weight, the read of what it wrote (one
+    kernel); keeps the written streams in `pending.value` and returns the normed rows or None."""
+    x = materialized(pending.x)
+    _need(x, "streams: x", torch.float32)
+    y, splits = _sublayer_output(pending.y)
+    width, streams = int(y.shape[-1]), pending.streams
+    if x.shape[1] not in (width, streams * width):
+        raise KernelError(f"streams: rows of {x.shape[1]} for {streams} streams of {width}")
+    for name, t, n in (("mix", pending.mix, streams * streams), ("out", pending.out_w, streams)):
+        _need(t, f"streams: {name}", torch.float32)
+        if t.numel() != n:
+            raise KernelError(f"streams: {name} has {t.numel()} numbers, {n} are needed")
+    pending.value, normed = _streams_launch(x, x.shape[1] // width, streams, width, y, splits, pending.mix, pending.out_w,
+                                            in_w, norm_w, eps, out_dtype)
+    return normed
+
+
+def streams_write(x, y, mix: torch.Tensor, out_w: torch.Tensor, streams: int):
+    """The streams after a sublayer: x'_t = sum_s mix[s, t] x_s + out_w[t] y, float32 [tokens, streams *
+    width]; x is [tokens, streams * width], or [tokens, width] for streams that are all equal. The
+    result is pending: the read that follows runs the write in its own kernel."""
+    return PendingStreams(x, y, mix, out_w, streams)
+
+
+def streams_read_norm(x, in_w, norm_w: torch.Tensor, eps: float, streams: int, out_dtype) -> torch.Tensor:
+    """RMS norm of u = sum_s in_w[s] x_s (in_w None: the plain sum) times norm_w, in `out_dtype`; x
+    float32 [tokens, streams * width] or [tokens, width] (equal streams), or a pending write."""
+    _need(norm_w, "streams_read_norm: norm weight", torch.float32)
+    if in_w is not None:
+        _need(in_w, "streams_read_norm: read weights", torch.float32)
+        if in_w.numel() != streams:
+            raise KernelError(f"streams_read_norm: {in_w.numel()} read weights for {streams} streams")
+    if isinstance(x, PendingStreams) and x.value is None:
+        if x.streams != streams or x.y.shape[-1] != norm_w.numel():
+            raise KernelError("streams_read_norm: the pending write has other streams than the read")
+        return _streams_step(x, in_w, norm_w, eps, out_dtype)
+    x = materialized(x)
+    _need(x, "streams_read_norm: x", torch.float32)
+    width = norm_w.numel()
+    if x.shape[1] not in (width, streams * width):
+        raise KernelError(f"streams_read_norm: rows of {x.shape[1]} for {streams} streams of {width}")
+    return _streams_launch(x, x.shape[1] // width, streams, width, None, 0, None, None, in_w, norm_w, eps, out_dtype)[1]
+
+
+def route(logits, correction, top: int, groups: int = 0, keep: int = 0, score: str = "softmax", eps: float = 0.0,
+          scale: float = 1.0):
+    """Chooses `top` experts per token from float32 router logits [tokens, experts] (csrc/routing.cu):
+    scores softmax (or sigmoid) of the logits, the choice by score + correction among the experts of
+    the `keep` best of `groups` groups (0: all experts), weights score / (sum of the chosen + eps) *
+    scale. -> (chosen int32 [tokens, top], weights float32 [tokens, top], dense float32 [tokens,
+    experts] with the weights at the chosen experts' columns and 0 elsewhere)."""
+    logits = materialized(logits)
+    _need(logits, "route: logits", torch.float32)
+    tokens, total = logits.shape
+    if correction is not None:
+        _need(correction, "route: correction", torch.float32)
+        if correction.numel() != total:
+            raise KernelError(f"route: a correction of {correction.numel()} numbers for {total} experts")
+    if score not in ("softmax", "sigmoid"):
+        raise KernelError(f"route: score '{score}' (softmax, sigmoid)")
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
+    dense = torch.empty((tokens, total), dtype=torch.float32, device=logits.device)
+    lib = _lib("routing")
+    _check(lib, lib.pae_route(_ptr(chosen), _ptr(weights), _ptr(dense), _ptr(logits), _ptr(correction), tokens, total, top,
+                              groups, keep, 1 if score == "sigmoid" else 0, float(eps), float(scale), _stream()))
+    return chosen, weights, dense
+
+
+def weight_expert_columns(hidden, dense, ff: int, experts: int) -> torch.Tensor:
+    """hidden[t, e * ff + j] *= dense[t, e] for e < experts, in place; further columns stay."""
+    hidden = materialized(hidden)
+    _need(hidden, "weight_expert_columns: hidden")
+    _need(dense, "weight_expert_columns: weights", torch.float32)
+    lib = _lib("routing")
+    _check(lib, lib.pae_weight_expert_columns(_ptr(hidden), _ptr(dense), dense.shape[1], hidden.shape[0], hidden.shape[1], ff,
+                                              experts, _code(hidden), _stream()))
+    return hidden
+
+
+def identity_share(x, dense, first: int, count: int, residual=None) -> torch.Tensor:
+    """float32 x[t, :] * sum(dense[t, first : first + count]) (+ a float32 residual): what experts that
+    return their input add."""
+    x = materialized(x)
+    residual = materialized(residual)
+    _need(x, "identity_share: x")
+    if residual is not None:
+        _need(residual, "identity_share: residual", torch.float32)
+    _need(dense, "identity_share: weights", torch.float32)
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    lib = _lib("routing")
+    _check(lib, lib.pae_identity_share(_ptr(out), _ptr(x), _ptr(dense), _ptr(residual), dense.shape[1], first, count, x.shape[0], x.shape[1],
+                                       _code(x), _stream()))
     return out

@@ -27,6 +27,8 @@ What each kind of part must provide:
                 `forward(ctx, x, residual, cache) -> residual + mixer(x)` where
                 `cache` is the `EntryCache` of the schedule entry that runs.
   feed-forward  `forward(ctx, x, residual) -> residual + ff(x)`.
+  connection    `forward(ctx, streams, y) -> streams`: how a sublayer's output y goes back into
+                several residual streams.
   block         `roles`: which parts a layer of this kind has and the registry each
                 comes from ({"mixer_norm": "norm", "mixer": "mixer", ...}); the
                 model builds exactly these from the `LayerSpec` and hands them to
@@ -59,6 +61,8 @@ class TensorSpec:
     taps     the weights of a short convolution: held in float32; drawn uniformly from (-1, 1).
     rate     a small positive constant (the slope inside a logarithm): held in float32;
              drawn uniformly from (0, 0.1).
+    mixing   a small square matrix that mixes residual streams: held in float32; drawn as the
+             identity + N(0, 0.02).
 
     A dimension of -1 in `shape` is whatever the checkpoint has (the part reads the size from
     its tensor); `random_size` is what the random-weights mode draws there.
@@ -196,10 +200,11 @@ POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+CONNECTIONS = Registry("connection")
 
 REGISTRIES: dict[str, Registry] = {
     "mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position_encoding": POSITION_ENCODINGS,
-    "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS,
+    "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS, "connection": CONNECTIONS,
 }
 
 

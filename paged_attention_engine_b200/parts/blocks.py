@@ -45,3 +45,32 @@ class MixerResidual(Block):
         # the norm may sum a product that is still in its splits; `materialized` then hands out that sum
         normed = layer.norm.forward(ctx, hidden)
         return layer.mixer.forward(ctx, normed, ctx.ops.materialized(hidden), cache)
+
+
+@BLOCKS.register("hyper_connected")
+class HyperConnected(Block):
+    """Several residual streams instead of one. Each sublayer reads a weighted sum of the streams
+    through its norm (a `stream_rms_norm`), and its `connection` part writes the output back: every
+    new stream is a mix of the old ones plus a multiple of the output. The sublayers get no residual
+    and leave their output in float32; the write stays pending until the next read, which does
+    both in one kernel."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_merge": "connection",
+             "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_merge": "connection"}
+
+    def forward(self, ctx, hidden, layer, cache):
+        out = layer.mixer.forward(ctx, layer.mixer_norm.forward(ctx, hidden), None, cache)
+        hidden = layer.mixer_merge.forward(ctx, ctx.ops.materialized(hidden), out)
+        out = layer.feed_forward.forward(ctx, layer.feed_forward_norm.forward(ctx, hidden), None)
+        return layer.feed_forward_merge.forward(ctx, ctx.ops.materialized(hidden), out)
+
+
+@BLOCKS.register("hyper_connected_mixer")
+class HyperConnectedMixer(Block):
+    """A hyper-connected layer without a feed-forward."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_merge": "connection"}
+
+    def forward(self, ctx, hidden, layer, cache):
+        out = layer.mixer.forward(ctx, layer.mixer_norm.forward(ctx, hidden), None, cache)
+        return layer.mixer_merge.forward(ctx, ctx.ops.materialized(hidden), out)

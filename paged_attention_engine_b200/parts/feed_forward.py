@@ -50,9 +50,10 @@ class SwiGLU(Part):
 @FEED_FORWARDS.register("dense_mlp")
 class DenseMLP(Part):
     """down(act(up(x))) without biases. params: hidden_size, intermediate_size, activation
-    ("gelu_erf": 0.5 z (1 + erf(z / sqrt 2)), or "gelu_tanh"). tensors: up.weight, down.weight.
-    The residual may be float32 while x is in the engine's dtype: the down projection adds it in
-    its epilogue and leaves the residual's dtype."""
+    ("gelu_erf": 0.5 z (1 + erf(z / sqrt 2)), "gelu_tanh", or "relu2": max(z, 0)^2). tensors:
+    up.weight, down.weight. The residual may be float32 while x is in the engine's dtype: the down
+    projection adds it in its epilogue and leaves the residual's dtype; without a residual (a
+    caller that sums by itself) the output leaves in float32."""
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
@@ -71,7 +72,7 @@ class DenseMLP(Part):
     def forward(self, ctx, x, residual):
         ops = self.ops
         hidden = ops.linear(x, self.up_weight, None, activation=self.activation)     # the activation in the product's epilogue
-        return ops.linear(hidden, self.down_weight, None, residual, out_dtype=residual.dtype if residual is not None else None)
+        return ops.linear(hidden, self.down_weight, None, residual, out_dtype=residual.dtype if residual is not None else torch.float32)
 
 
 @FEED_FORWARDS.register("clamped_glu")
@@ -105,3 +106,80 @@ class ClampedGLU(Part):
         gate_up = ops.linear(x, self.gate_up_weight, self.gate_up_bias, None, out_dtype=torch.float32)
         hidden = ops.clamped_glu(gate_up, self.limit, self.alpha, self.runtime.dtype)
         return ops.linear(hidden, self.down_weight, self.down_bias, residual, out_dtype=residual.dtype)
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(Part):
+    """A mixture of experts down_e(act(up_e(x))) without biases, of which each token uses `top`.
+
+    Router logits z = W_router x in float32; scores s = softmax(z) (or sigmoid) over all experts;
+    the choice goes by s + correction (a stored vector) among the experts of the `group_keep` best of
+    `group_count` groups of neighbours (a group's score is its largest choice score), the weights
+    are the chosen s / (their sum + weight_eps) * weight_scale. The last `identity_experts` router
+    outputs are experts without tensors that return x itself. A shared expert of its own size runs
+    for every token.
+
+    params: hidden_size, intermediate_size, activation, num_experts (with tensors), identity_experts,
+    top, score ("softmax" or "sigmoid"), choice_correction (bool), group_count (0: none), group_keep,
+    weight_eps, weight_scale, shared_size (0: none).
+    tensors: router [num_experts + identity_experts, hidden], correction (the same count),
+    e<i>.up [intermediate, hidden], e<i>.down [hidden, intermediate], shared.up, shared.down.
+
+    The experts run as two products over all tokens: every expert's up projection (and the shared
+    expert's) side by side, each expert's hidden columns multiplied by the token's weight for
+    it (0 where it was not chosen), and one down projection over all of them, which therefore
+    adds the chosen experts' outputs, weighted, and the shared expert's. What the identity experts
+    add, x times their weights, enters that product's epilogue with the residual."""
+
+    @classmethod
+    def _sizes(cls, spec: PartSpec):
+        p = spec.params
+        return (int(p["hidden_size"]), int(p["intermediate_size"]), int(p["num_experts"]), int(p.get("identity_experts") or 0),
+                int(p.get("shared_size") or 0))
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
+        hidden, ff, experts, identity, shared = cls._sizes(spec)
+        name = spec.tensor_name
+        out = [TensorSpec(name("router"), (experts + identity, hidden), "matrix")]
+        if spec.params.get("choice_correction"):
+            out.append(TensorSpec(name("correction"), (experts + identity,), "vector"))
+        for e in range(experts):
+            out += [TensorSpec(name(f"e{e}.up"), (ff, hidden), "matrix"), TensorSpec(name(f"e{e}.down"), (hidden, ff), "matrix")]
+        if shared:
+            out += [TensorSpec(name("shared.up"), (shared, hidden), "matrix"), TensorSpec(name("shared.down"), (hidden, shared), "matrix")]
+        return out
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        p = spec.params
+        self.hidden, self.ff, self.experts, self.identity, self.shared = self._sizes(spec)
+        self.top = int(p["top"])
+        self.score = str(p.get("score", "softmax"))
+        self.group_count, self.group_keep = int(p.get("group_count") or 0), int(p.get("group_keep") or 0)
+        self.weight_eps, self.weight_scale = float(p.get("weight_eps") or 0.0), float(p.get("weight_scale", 1.0))
+        self.activation = str(p.get("activation", "relu2"))
+        name = spec.tensor_name
+        self.router = tensors.pop(name("router"))
+        self.correction = tensors.pop(name("correction")) if p.get("choice_correction") else None
+        ups = [tensors.pop(name(f"e{e}.up")) for e in range(self.experts)]
+        downs = [tensors.pop(name(f"e{e}.down")) for e in range(self.experts)]
+        if self.shared:
+            ups.append(tensors.pop(name("shared.up")))
+            downs.append(tensors.pop(name("shared.down")))
+        self.up_weight = torch.cat(ups, dim=0).contiguous()          # [experts * ff + shared, hidden]
+        self.down_weight = torch.cat(downs, dim=1).contiguous()      # [hidden, experts * ff + shared]
+
+    def forward(self, ctx, x, residual):
+        ops = self.ops
+        x = ops.materialized(x)
+        logits = ops.linear(x, self.router, None, None, out_dtype=torch.float32)
+        _, _, dense = ops.route(logits, self.correction, self.top, self.group_count, self.group_keep, self.score,
+                                self.weight_eps, self.weight_scale)
+        hidden = ops.linear(x, self.up_weight, None, activation=self.activation)
+        hidden = ops.weight_expert_columns(hidden, dense, self.ff, self.experts)
+        out_dtype = residual.dtype if residual is not None else torch.float32
+        if self.identity:
+            # float32, as the residual of such a model is
+            residual, out_dtype = ops.identity_share(x, dense, self.experts, self.identity, residual), torch.float32
+        return ops.linear(hidden, self.down_weight, None, residual, out_dtype=out_dtype)

@@ -11,6 +11,10 @@ q[n] . k[n] = A_n . c + q_rotated[n] . shared, so every head attends the same la
 one key/value head whose key is [c | shared] and whose value is c; the value expansion W_uv[n]
 is applied to the attention's output over the latent. A layer may read the latent of an
 earlier layer (through the schedule's `cache_from`): it has no down projection and writes nothing.
+
+Two options. The queries may go through a latent of their own: c_q = RMSnorm(W_dq h) with a
+weight, q = W_uq c_q (`q_rank`). And every head's output may be multiplied by one sigmoid of a
+projection of h (`head_gate`, a gate per head, not per channel) before the output projection.
 """
 
 from __future__ import annotations
@@ -25,8 +29,10 @@ from .base import MIXERS, CacheNeed, Part, TensorSpec
 class LatentAttention(Part):
     """params: hidden_size, num_heads, head_dim (unrotated channels), rot_dim, value_dim, kv_rank,
     scale, norm_eps, own_latent (False: the layer reads another entry's cache), window (0: causal),
-    position_encoding (a dict with its `kind`; its `dims` equal rot_dim).
-    tensors: q [heads * (head_dim + rot_dim), hidden]; dkv [kv_rank + rot_dim, hidden] and dkv.norm
+    position_encoding (a dict with its `kind`; its `dims` are at most rot_dim: the leading channels
+    of the rotated part turn), q_rank (0 or absent: no query latent), head_gate (False or absent: none).
+    tensors: q [heads * (head_dim + rot_dim), hidden], or with a query latent dq [q_rank, hidden],
+    dq.norm [q_rank] and uq [heads * (head_dim + rot_dim), q_rank]; g [heads, hidden] with a gate; dkv [kv_rank + rot_dim, hidden] and dkv.norm
     [kv_rank] with a latent of its own; uk [heads * head_dim, kv_rank]; uv [heads * value_dim, kv_rank];
     o [hidden, heads * value_dim]."""
 
@@ -40,7 +46,14 @@ class LatentAttention(Part):
         hidden = int(spec.params["hidden_size"])
         heads, d, r, dv, c = cls._sizes(spec)
         name = spec.tensor_name
-        out = [TensorSpec(name("q"), (heads * (d + r), hidden), "matrix")]
+        q_rank = int(spec.params.get("q_rank") or 0)
+        if q_rank:
+            out = [TensorSpec(name("dq"), (q_rank, hidden), "matrix"), TensorSpec(name("dq.norm"), (q_rank,), "scale"),
+                   TensorSpec(name("uq"), (heads * (d + r), q_rank), "matrix")]
+        else:
+            out = [TensorSpec(name("q"), (heads * (d + r), hidden), "matrix")]
+        if spec.params.get("head_gate"):
+            out.append(TensorSpec(name("g"), (heads, hidden), "matrix"))
         if spec.params.get("own_latent", True):
             out += [TensorSpec(name("dkv"), (c + r, hidden), "matrix"), TensorSpec(name("dkv.norm"), (c,), "scale")]
         return out + [TensorSpec(name("uk"), (heads * d, c), "matrix"), TensorSpec(name("uv"), (heads * dv, c), "matrix"),
@@ -68,21 +81,27 @@ class LatentAttention(Part):
         self.norm_eps = float(p["norm_eps"])
         self.own_latent = bool(p.get("own_latent", True))
         name = spec.tensor_name
-        q_weight = tensors.pop(name("q"))
-        self.latent_norm = None
+        self.q_rank = int(p.get("q_rank") or 0)
+        self.head_gate = bool(p.get("head_gate"))
+        # One projection for q (or the query latent) | gates | down: the columns of its output in that order.
+        rows = [tensors.pop(name("dq" if self.q_rank else "q"))]
+        self.q_cols = int(rows[0].shape[0])
+        if self.head_gate:
+            rows.append(tensors.pop(name("g")))
+        self.latent_norm = self.query_norm = self.uq_weight = None
+        if self.q_rank:
+            self.query_norm, self.uq_weight = tensors.pop(name("dq.norm")), tensors.pop(name("uq"))
         if self.own_latent:
-            # One projection for q | down: the columns of its output in that order.
-            self.in_weight = torch.cat([q_weight, tensors.pop(name("dkv"))], dim=0).contiguous()
+            rows.append(tensors.pop(name("dkv")))
             self.latent_norm = tensors.pop(name("dkv.norm"))
-        else:
-            self.in_weight = q_weight
+        self.in_weight = torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else rows[0]
         # [heads, kv_rank, head_dim]: head n's key expansion transposed, so that A_n is a product like any other.
         self.uk_t = tensors.pop(name("uk")).view(heads, d, c).transpose(1, 2).contiguous()
         self.uv = tensors.pop(name("uv")).view(heads, dv, c).contiguous()
         self.o_weight = tensors.pop(name("o"))
         built = self.build_sub_parts(tensors)
         self.position_encoding = built[0] if built else None
-        if self.position_encoding is not None and self.position_encoding.dims != r:
+        if self.position_encoding is not None and self.position_encoding.dims > r:
             raise ValueError(f"latent_attention: {self.position_encoding.dims} rotated channels, rot_dim is {r}")
 
     def forward(self, ctx, x, residual, cache):
@@ -93,13 +112,24 @@ class LatentAttention(Part):
             raise ValueError("latent_attention: a layer with a latent of its own writes its cache, one without reads another's")
         proj = ops.linear(x, self.in_weight, None, None, out_dtype=torch.float32)
         table = self.position_encoding.table(ctx) if self.position_encoding is not None else None
-        # queries [tokens, heads, d + r] with their rotated channels turned; the token's latent row into its page
-        q = ops.head_prep(
-            proj, q_off=0, k_off=heads * (d + r), v_off=0, heads=heads, kv_heads=1 if self.own_latent else 0,
-            q_dim=d + r, k_dim=c + r, value_dim=0, q_norm=None, k_norm=self.latent_norm, q_span=0, k_span=c,
-            eps=self.norm_eps, table=table, interleaved=True, q_rot0=d, k_rot0=c,
-            slots=group.slots if self.own_latent else None, keys=cache.keys, values=None, page_size=cache.page_size,
-            out_dtype=self.runtime.dtype)
+        gate_off = self.q_cols
+        k_off = gate_off + (heads if self.head_gate else 0)
+        prep = dict(q_dim=d + r, k_dim=c + r, value_dim=0, q_norm=None, k_norm=self.latent_norm, q_span=0, k_span=c,
+                    eps=self.norm_eps, table=table, interleaved=True, q_rot0=d, k_rot0=c, keys=cache.keys, values=None,
+                    page_size=cache.page_size, out_dtype=self.runtime.dtype)
+        slots = group.slots if self.own_latent else None
+        if self.q_rank:
+            # the token's latent row into its page; then the queries from their own normed latent
+            proj = ops.materialized(proj)
+            if self.own_latent:
+                ops.head_prep(proj, q_off=0, k_off=k_off, v_off=0, heads=0, kv_heads=1, slots=slots, **prep)
+            query_latent = ops.rms_norm_columns(proj, 0, self.q_rank, self.query_norm, self.norm_eps, self.runtime.dtype)
+            queries = ops.linear(query_latent, self.uq_weight, None, None, out_dtype=torch.float32)
+            q = ops.head_prep(queries, q_off=0, k_off=0, v_off=0, heads=heads, kv_heads=0, slots=None, **prep)
+        else:
+            # queries [tokens, heads, d + r] with their rotated channels turned; the token's latent row into its page
+            q = ops.head_prep(proj, q_off=0, k_off=k_off, v_off=0, heads=heads, kv_heads=1 if self.own_latent else 0,
+                              slots=slots, **prep)
         # [A_n | rotated channels] per head: the query against the latent rows
         q = ops.linear_heads(q, self.uk_t, heads, in_stride=d + r, tail=r)
         over_latent = ops.paged_attention_scored(
@@ -107,4 +137,7 @@ class LatentAttention(Part):
             cache.page_size, ctx.max_q_len, self.scale, window=self.window, max_kv_len=ctx.max_kv_len,
             num_single=ctx.num_single)
         out = ops.linear_heads(over_latent, self.uv, heads, in_stride=c, tail=0)
-        return ops.linear(out, self.o_weight, None, residual, out_dtype=residual.dtype)
+        if self.head_gate:
+            out = ops.sigmoid_gate(out, proj, gate_off, group=dv)
+        # without a residual (a caller that sums by itself) the output leaves in float32
+        return ops.linear(out, self.o_weight, None, residual, out_dtype=residual.dtype if residual is not None else torch.float32)

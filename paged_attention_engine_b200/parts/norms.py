@@ -9,19 +9,25 @@ from ..config.model_spec import PartSpec
 from .base import NORMS, Part, TensorSpec
 
 
+def offset_weight(weight, offset):
+    """The weight a norm multiplies by: what the checkpoint stores, plus `offset` (float32)."""
+    return weight + float(offset) if offset else weight
+
+
 @NORMS.register("rms_norm")
 class RMSNorm(Part):
     """params: size, eps, out ("engine": the result is in the engine's dtype whatever x is, as a
-    float32 residual stream needs; default: x's dtype). tensors: weight [size]."""
+    float32 residual stream needs; default: x's dtype), weight_offset (c: the checkpoint stores
+    w - c, as a weight kept around zero does with c = 1; default 0). tensors: weight [size]."""
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
-        return [TensorSpec(spec.tensor_name("weight"), (int(spec.params["size"]),), "scale")]
+        return [TensorSpec(spec.tensor_name("weight"), (int(spec.params["size"]),), "vector" if spec.params.get("weight_offset") else "scale")]
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
         self.eps = float(spec.params["eps"])
-        self.weight = tensors[spec.tensor_name("weight")]
+        self.weight = offset_weight(tensors[spec.tensor_name("weight")], spec.params.get("weight_offset"))
         self.out_dtype = runtime.dtype if spec.params.get("out") == "engine" else None
 
     def forward(self, ctx, x):
@@ -54,3 +60,29 @@ class LayerNorm(Part):
 
     def forward(self, ctx, x):
         return self.ops.layer_norm(x, self.weight, self.bias, self.eps, self.out_dtype)
+
+
+@NORMS.register("stream_rms_norm")
+class StreamRMSNorm(Part):
+    """The read of a decoder with several residual streams: u = sum_s read[s] x_s, then u /
+    sqrt(mean(u^2) + eps) * weight in the engine's dtype. x is float32 [tokens, streams * size]
+    (or [tokens, size]: streams that are all equal). params: size, streams, eps, weight_offset (as
+    for rms_norm), weighted_read (False: the plain sum of the streams, no `read` tensor).
+    tensors: weight [size], read [streams]."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
+        out = [TensorSpec(spec.tensor_name("weight"), (int(spec.params["size"]),), "vector" if spec.params.get("weight_offset") else "scale")]
+        if spec.params.get("weighted_read", True):
+            out.append(TensorSpec(spec.tensor_name("read"), (int(spec.params["streams"]),), "scale"))
+        return out
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.eps = float(spec.params["eps"])
+        self.streams = int(spec.params["streams"])
+        self.weight = offset_weight(tensors[spec.tensor_name("weight")], spec.params.get("weight_offset"))
+        self.read = tensors[spec.tensor_name("read")] if spec.params.get("weighted_read", True) else None
+
+    def forward(self, ctx, x):
+        return self.ops.streams_read_norm(x, self.read, self.weight, self.eps, self.streams, self.runtime.dtype)

@@ -100,7 +100,7 @@ def place(tensor: torch.Tensor, spec: TensorSpec, dtype: torch.dtype, device) ->
         return tensor.to(device=device, dtype=torch.int32).contiguous()
     if not tensor.dtype.is_floating_point:
         raise WeightsError(f"{spec.name}: stored as {tensor.dtype}, a floating-point tensor is read")
-    if spec.kind in ("vector", "scale", "taps", "rate"):
+    if spec.kind in ("vector", "scale", "taps", "rate", "mixing"):
         return tensor.to(device=device, dtype=torch.float32).contiguous()
     if dtype == torch.bfloat16 and tensor.dtype in (torch.float32, torch.float64):
         return tensor.to(device=device, dtype=torch.float32).contiguous()

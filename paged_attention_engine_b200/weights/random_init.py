@@ -2,7 +2,7 @@
 configuration and a seed.
 
 The draw follows the tensor's kind: matrices and biases N(0, 0.02), norm weights
-1 + N(0, 0.02), integer tables uniform, convolution taps uniform in (-1, 1), rates uniform
+1 + N(0, 0.02), stream-mixing matrices the identity + N(0, 0.02), integer tables uniform, convolution taps uniform in (-1, 1), rates uniform
 in (0, 0.1). Tensors are drawn in the order of their
 sorted names from one seeded CPU generator, so a folder is the same wherever it is
 written. (The reference's only random model is a test fixture: tests/tiny_model.py:21-50.)
@@ -31,6 +31,8 @@ def draw(spec, generator: torch.Generator, device="cpu") -> torch.Tensor:
     if spec.kind == "rate":
         return torch.rand(shape, generator=generator, device=device, dtype=torch.float32) * 0.1
     t = torch.randn(shape, generator=generator, device=device, dtype=torch.float32) * STD
+    if spec.kind == "mixing":
+        return t + torch.eye(shape[0], shape[1], device=device, dtype=torch.float32)
     return t + 1.0 if spec.kind == "scale" else t
 
 
