@@ -294,6 +294,36 @@ def zugarax_config(size: dict, window: int = 1024, kv_rank: int = 512, rot_dim: 
             "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": layers}
 
 
+def zugarax_latent_config(size: dict, kv_rank: int = 512, rot_dim: int = 64) -> dict:
+    """Zugarax with latent attention in every layer, each with a latent of its own: the closest of
+    the other architectures to Pukerax layer by layer (the same cached row per token and layer)."""
+    raw = zugarax_config(size, kv_rank=kv_rank, rot_dim=rot_dim)
+    latent = next(layer for layer in raw["layers"] if layer["type"] == "latent_attention")
+    latent = json.loads(json.dumps(latent))
+    latent["mixer"].pop("kv_from", None)
+    raw["layers"] = [json.loads(json.dumps(latent)) for _ in range(size["layers"])]
+    return raw
+
+
+def pukerax_config(size: dict, kv_rank: int = 512, rot_dim: int = 64, streams: int = 4, experts: int = 30, identity: int = 2,
+                   top: int = 6) -> dict:
+    """Pukerax at the layer sizes of `size`: latent attention (the same latent and rotated part as
+    Zugarax's, a query latent of half the width) in every layer, four hyper-connected streams; the
+    first layer's feed-forward is dense, the others route each token to `top` of `experts` experts
+    of an eighth of the dense width (and `identity` experts that return their input; four groups of
+    which two are kept) beside a shared expert of a quarter of it, so that a token's feed-forward
+    products are as many as the dense layer's."""
+    d = size["dim"]
+    mixer = {"heads": size["heads"], "dim": d, "rot_dim": rot_dim, "vdim": d, "kv_rank": kv_rank, "q_rank": size["width"] // 2,
+             "scale": (d + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
+    dense = {"kind": "dense", "ff": size["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": size["ff"] // 8}, "shared": {"ff": size["ff"] // 4},
+              "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "latent_attention", "mixer": mixer, "mlp": dense if i == 0 else routed} for i in range(size["layers"])]
+    return {"architecture": "Pukerax", "vocab": size["vocab"], "width": size["width"], "streams": streams, "norm": {"eps": 1e-6},
+            "layers": json.loads(json.dumps(layers))}
+
+
 def step_cache_bytes(cache, contexts) -> float:
     """Cache bytes that a decode step reads: per page group the keys and values a request can see
     (all of its context, or the window and the kept first keys), and every recurrent state
@@ -308,18 +338,22 @@ def step_cache_bytes(cache, contexts) -> float:
     return total
 
 
-def bidonex_beside_qwen2(torch, peak: dict, steps: int, warmup: int, sizes, with_zugarax: bool = False) -> dict:
+def bidonex_beside_qwen2(torch, peak: dict, steps: int, warmup: int, sizes, with_zugarax: bool = False, pukerax: bool = False) -> dict:
     """Prefill and decode of the architectures at equal layer sizes; `with_zugarax` puts Zugarax
-    in front of Bidonex (the closest of the others: a float32 stream, windows, a recurrent layer) and Qwen2."""
+    in front of Bidonex (the closest of the others: a float32 stream, windows, a recurrent layer) and Qwen2;
+    `pukerax` times Pukerax beside Zugarax with latent attention in every layer (the closest to it) and Qwen2."""
     from paged_attention_engine_b200.engine.llm import Engine
     from paged_attention_engine_b200.sampling import SamplingRow
 
-    out: dict = {"only": "zugarax" if with_zugarax else "bidonex", "peaks": peak["source"], "sizes": {}}
+    out: dict = {"only": "pukerax" if pukerax else "zugarax" if with_zugarax else "bidonex", "peaks": peak["source"], "sizes": {}}
     for name in sizes:
         bidonex, qwen = bidonex_pair(BIDONEX_SIZES[name])
         rows: dict = {}
         archs = (("zugarax", zugarax_config(BIDONEX_SIZES[name])),) if with_zugarax else ()
-        for arch, raw in archs + (("bidonex", bidonex), ("qwen2", qwen)):
+        archs = archs + (("bidonex", bidonex), ("qwen2", qwen))
+        if pukerax:
+            archs = (("pukerax", pukerax_config(BIDONEX_SIZES[name])), ("zugarax_latent", zugarax_latent_config(BIDONEX_SIZES[name])), ("qwen2", qwen))
+        for arch, raw in archs:
             engine = Engine.from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
             row: dict = {"layers": BIDONEX_SIZES[name]["layers"], "weight_gb": round(engine.weight_bytes() / 1e9, 3)}
             for tokens in (512, 2048, 8192):
@@ -753,9 +787,9 @@ def main() -> int:
                         help="layer sizes for --only decode / prefill (the headline line is always the 1.5B shape)")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context length for --only decode")
     parser.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
-    parser.add_argument("--arch", choices=("qwen2", "bidonex", "zugarax"), default="qwen2",
+    parser.add_argument("--arch", choices=("qwen2", "bidonex", "zugarax", "zugarax_latent", "pukerax"), default="qwen2",
                         help="with --only decode / prefill: the architecture that runs at the --shape's layer sizes")
-    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b", "bidonex", "zugarax"), default="all",
+    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b", "bidonex", "zugarax", "pukerax"), default="all",
                         help="time one part only (for profiling); the JSON line then holds that part alone")
     args = parser.parse_args()
 
@@ -784,9 +818,10 @@ def main() -> int:
     if args.only == "pressure32b":
         print(json.dumps(pressure_32b(torch, args.layers_32b)))
         return 0
-    if args.only in ("bidonex", "zugarax"):
+    if args.only in ("bidonex", "zugarax", "pukerax"):
         sizes = ("1.5b", "7b") if args.shape == "1.5b" else (args.shape,)
-        print(json.dumps(bidonex_beside_qwen2(torch, peak, args.steps, warmup, sizes, with_zugarax=args.only == "zugarax")))
+        print(json.dumps(bidonex_beside_qwen2(torch, peak, args.steps, warmup, sizes, with_zugarax=args.only == "zugarax",
+                                              pukerax=args.only == "pukerax")))
         return 0
     if args.only == "products":
         for row in time_products({"1.5b": MODEL, "7b": MODEL_7B, "32b": MODEL_32B}[args.shape], args.batch, torch, peak):
@@ -797,7 +832,7 @@ def main() -> int:
     if args.only != "all" and args.shape != "1.5b" and args.layers == MODEL["num_hidden_layers"]:
         args.layers = model["num_hidden_layers"]
     model["num_hidden_layers"] = args.layers
-    if args.arch in ("bidonex", "zugarax") and args.only in ("decode", "prefill"):
+    if args.arch != "qwen2" and args.only in ("decode", "prefill"):
         if args.shape not in BIDONEX_SIZES:
             print(f"bench.py: --arch {args.arch} has the shapes {', '.join(BIDONEX_SIZES)}")
             return 2
@@ -806,7 +841,8 @@ def main() -> int:
             size["layers"] = args.layers
         args.layers = size["layers"]
         bidonex, model = bidonex_pair(size)
-        engine = Engine.from_random(zugarax_config(size) if args.arch == "zugarax" else bidonex, seed=0, dtype="bfloat16", device="cuda:0")
+        raw = {"zugarax": zugarax_config, "zugarax_latent": zugarax_latent_config, "pukerax": pukerax_config}.get(args.arch, lambda size: bidonex)(size)
+        engine = Engine.from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
     else:
         engine = Engine.from_random(model, seed=0, dtype="bfloat16", device="cuda:0")
 

@@ -22,15 +22,33 @@ namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 outputs each
 
+// The activations a product can apply to its own output (the sum, rounded to the output's type first):
+// 1 exact GELU, 2 tanh GELU, 3 the square of max(z, 0).
+__device__ __forceinline__ float activation_of(float z, int kind) {
+  if (kind == 1) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+  if (kind == 3) { z = fmaxf(z, 0.f); return z * z; }
+  return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
 template <typename TA, typename TW, typename TO, typename TAcc>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, const TA* __restrict__ x,
                                                         const TW* __restrict__ w, const float* __restrict__ bias,
-                                                        const TO* __restrict__ residual, int M, int N, int K) {
+                                                        const TO* __restrict__ residual, int M, int N, int K,
+                                                        const int* __restrict__ group_tiles, int tile, int activation) {
   dependent_launch_prologue();
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  if (group_tiles != nullptr) {
+    // Grouped: w is one [N, K] matrix per group; the rows of tile j (of `tile` rows, a multiple of BM)
+    // multiply matrix group_tiles[2 j], and only the tile's first group_tiles[2 j + 1] rows count.
+    const int j = m0 / tile, g = group_tiles[2 * j];
+    if (g < 0) return;
+    w += (size_t)g * N * K;
+    M = min(M, j * tile + group_tiles[2 * j + 1]);
+    if (m0 >= M) return;
+  }
   const int tx = tid % 16, ty = tid / 16;      // outputs rows ty*4.., cols tx*4..
   const int load_row = tid / 4, load_k = (tid % 4) * 4;
 
@@ -77,6 +95,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, co
       if (n >= N) continue;
       TAcc v = acc[i][j];
       if (bias != nullptr) v += (TAcc)bias[n];
+      if (activation != 0) v = (TAcc)activation_of(to_float(from_float<TO>((float)v)), activation);
       if (residual != nullptr) v += (TAcc)to_float(residual[(size_t)m * N + n]);
       out[(size_t)m * N + n] = from_float<TO>((float)v);
     }
@@ -85,9 +104,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, co
 
 template <typename TA, typename TW, typename TO, typename TAcc = float>
 int launch(void* out, const void* x, const void* w, const float* bias, const void* residual, int M, int N, int K,
-           cudaStream_t s) {
+           cudaStream_t s, const int* group_tiles = nullptr, int tile = 0, int activation = 0) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  launch_kernel(gemm_simt_kernel<TA, TW, TO, TAcc>, grid, 256, 0, s, (TO*)out, (const TA*)x, (const TW*)w, bias, (const TO*)residual, M, N, K);
+  launch_kernel(gemm_simt_kernel<TA, TW, TO, TAcc>, grid, 256, 0, s, (TO*)out, (const TA*)x, (const TW*)w, bias, (const TO*)residual, M, N, K,
+                group_tiles, tile, activation);
   return check_launch("linear_simt");
 }
 
@@ -110,6 +130,27 @@ PAE_EXPORT int pae_linear_simt(void* out, const void* x, const void* w, const fl
     case 100: return launch<bf, float, float>(out, x, w, bias, residual, M, N, K, s);
     default:
       return fail(1, "linear_simt: element types x=%d w=%d out=%d are not supported", x_dtype, w_dtype, out_dtype);
+  }
+}
+
+// The grouped product on the CUDA cores: out[row, n] = act(x[row, k] . w[g(row)][n, k]^T) for rows sorted
+// by matrix in tiles of `tile` rows (a multiple of 64); tiles int32 [max_tiles, 2]: each tile's matrix
+// (negative: skipped) and how many of its rows count. x and w of one type (float32: sums in double),
+// out of that type or float32.
+PAE_EXPORT int pae_linear_grouped_simt(void* out, const void* x, const void* w, const int* tiles, int max_tiles, int tile, int n, int k,
+                                       int x_dtype, int out_dtype, int activation, void* stream) {
+  if (max_tiles == 0 || n == 0) return 0;
+  if (tile < BM || tile % BM) return fail(2, "linear_grouped_simt: tiles of %d rows are not a multiple of %d", tile, BM);
+  const long long rows = (long long)max_tiles * tile;
+  if (rows / BM > 65535) return fail(3, "linear_grouped_simt: %lld rows are more than one launch takes", rows);
+  cudaStream_t s = (cudaStream_t)stream;
+  using bf = __nv_bfloat16;
+  const int M = (int)rows;
+  switch (x_dtype * 10 + out_dtype) {
+    case 0: return launch<float, float, float, double>(out, x, w, nullptr, nullptr, M, n, k, s, tiles, tile, activation);
+    case 11: return launch<bf, bf, bf>(out, x, w, nullptr, nullptr, M, n, k, s, tiles, tile, activation);
+    case 10: return launch<bf, bf, float>(out, x, w, nullptr, nullptr, M, n, k, s, tiles, tile, activation);
+    default: return fail(1, "linear_grouped_simt: element types x=%d out=%d are not supported", x_dtype, out_dtype);
   }
 }
 

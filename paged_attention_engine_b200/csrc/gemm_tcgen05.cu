@@ -59,6 +59,11 @@ struct Params {
   __nv_bfloat16* keys;         // [pages, kv_heads, page_size, d]
   __nv_bfloat16* values;
   int heads, kv_heads, head_dim, page_size;
+  // Grouped (persistent kernel, NORMAL): the B operand is `groups` matrices of `rows_b` rows one after
+  // another; tile j of the A rows multiplies matrix group_tiles[2 j] (negative: the tile is
+  // skipped) and only its first group_tiles[2 j + 1] rows are stored.
+  const int* group_tiles;
+  int groups;
   int* error;
   int skip_kb;       // self-test of the give-up path only: the k-block (of each block's range) that is never loaded
 };
@@ -522,6 +527,12 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
         const int tile = item / planes, kb_first = (item % planes) * p.kb_per_split;
         const int kb_end = min(kb_first + p.kb_per_split, k_blocks);
         const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;     // neighbours share the weight tile
+        int b_row = tile_b * PBN;
+        if (p.group_tiles != nullptr) {
+          const int g = p.group_tiles[2 * tile_a];
+          if (g < 0) continue;
+          b_row += g * p.rows_b;
+        }
         for (int kb = kb_first; kb < kb_end; ++kb, ++it) {
           const int s = it % PSTAGES;
           if (it >= PSTAGES && !mbar_wait(empty_bar(s), ((it / PSTAGES) - 1) & 1, abort_flag, p.error, 1)) {
@@ -531,7 +542,7 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
           const uint32_t a_dst = base + s * P_STAGE_BYTES;
           mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, tile_a * BM);
-          tma_load_2d(a_dst + P_A_BYTES, &map_b, full_bar(s), kb * BK, tile_b * PBN);
+          tma_load_2d(a_dst + P_A_BYTES, &map_b, full_bar(s), kb * BK, b_row);
         }
       }
       if (*abort_flag) {
@@ -552,9 +563,11 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
       int local = 0, s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        if (p.group_tiles != nullptr && p.group_tiles[2 * ((item / planes) % tiles_a)] < 0) continue;
         const int acc = local & 1, use = local >> 1;
-        if (local >= 2) ok = mbar_wait(tmem_empty_bar(acc), (use - 1) & 1, abort_flag, p.error, 4);
+        ++local;
+        if (local > 2) ok = mbar_wait(tmem_empty_bar(acc), (use - 1) & 1, abort_flag, p.error, 4);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * ACC;
@@ -585,11 +598,17 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
     const int row_in_tile = quadrant * 32 + lane;
     int local = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++local) {
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const int tile = item / planes;
       const size_t plane_offset = (size_t)(item % planes) * p.rows_a * p.ld_out;
       const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
+      int rows_end = p.rows_a;                    // rows from here on are not stored
+      if (p.group_tiles != nullptr) {
+        if (p.group_tiles[2 * tile_a] < 0) continue;
+        rows_end = min(rows_end, tile_a * BM + p.group_tiles[2 * tile_a + 1]);
+      }
       const int acc = local & 1, use = local >> 1;
+      ++local;
       const int row = tile_a * BM + row_in_tile;
       // What the rotation needs of this thread's token is asked for before the wait for the
       // tile's MMAs: its place in its page and its first 16 cosines and sines.
@@ -649,7 +668,7 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
           float v[16];
           tmem_load16(lane_address + c0, v);
           const int col0 = tile_b * PBN + c0;
-          if (row < p.rows_a && col0 < p.rows_b) store_row_chunk(p, row, col0, v, plane_offset);
+          if (row < rows_end && col0 < p.rows_b) store_row_chunk(p, row, col0, v, plane_offset);
         }
       }
       tcgen05_fence_before();
@@ -700,7 +719,7 @@ int launch_persistent_with(const Params& p, const void* a, const void* b, int k,
   using T = PTile<PBN>;
   CUtensorMap map_a, map_b;
   if (int err = tensor_map(&map_a, a, p.rows_a, k, BM)) return err;
-  if (int err = tensor_map(&map_b, b, p.rows_b, k, PBN)) return err;
+  if (int err = tensor_map(&map_b, b, p.group_tiles != nullptr ? p.rows_b * p.groups : p.rows_b, k, PBN)) return err;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<PBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM_BYTES);
@@ -843,6 +862,32 @@ PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const
   if (n >= 128) return launch<128, NORMAL>(p, x, w, k, 1, s);
   if (n > 32) return launch<64, NORMAL>(p, x, w, k, 1, s);
   return launch<32, NORMAL>(p, x, w, k, 1, s);
+}
+
+// out[row, n] = x[row, k] . w[g(row)][n, k]^T for the rows of the tiles that `tiles` names: x
+// [max_tiles * 128, k] holds rows sorted by matrix and padded to whole tiles of 128 rows, w is
+// `groups` matrices [n, k] one after another, tiles int32 [max_tiles, 2] gives each tile's matrix
+// (negative: nothing is computed) and how many of its rows are stored. Rows that are not stored
+// keep what out held. out bfloat16 or float32; `activation` as in pae_linear_tcgen05.
+PAE_EXPORT int pae_linear_grouped_tcgen05(void* out, const void* x, const void* w, const int* tiles, int max_tiles, int groups,
+                                          int n, int k, int out_f32, int activation, int* error, void* stream) {
+  if (max_tiles == 0 || n == 0 || groups == 0) return 0;
+  if (int err = check_operands(x, w, k)) return err;
+  if (activation < 0 || activation > 3) return fail(2, "linear_grouped_tcgen05: activation %d", activation);
+  if ((long long)groups * n > 0x7fffffffLL) return fail(2, "linear_grouped_tcgen05: %d matrices of %d rows", groups, n);
+  Params p{};
+  p.activation = activation;
+  p.out = out;
+  p.rows_a = max_tiles * BM;
+  p.rows_b = n;
+  p.k_blocks = (k + BK - 1) / BK;
+  p.kb_per_split = p.k_blocks;
+  p.ld_out = n;
+  p.out_f32 = out_f32;
+  p.group_tiles = tiles;
+  p.groups = groups;
+  p.error = error;
+  return launch_persistent(p, x, w, k, (cudaStream_t)stream);
 }
 
 // How many float32 planes `pae_linear_tcgen05_planes` writes for this shape: 1 (call

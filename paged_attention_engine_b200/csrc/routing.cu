@@ -8,7 +8,7 @@
 //   weights  w_e = s_e / (sum of the chosen s + eps) * scale for the chosen, 0 for the others
 //
 // One warp per token; all arithmetic float32. The kernel leaves the chosen experts, their weights
-// and the dense row of weights [total experts] that the products' helpers read.
+// and, when asked, the dense row of weights [total experts].
 #include "common.cuh"
 
 #include <cfloat>
@@ -138,34 +138,94 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
   }
 }
 
-// h[t, e * ff + j] *= dense[t, e] for the routed experts' hidden columns (e < experts); columns
-// from experts * ff on (a shared expert's) stay. In place, rounded once.
-template <typename T>
-__global__ void weight_expert_columns_kernel(T* __restrict__ h, const float* __restrict__ dense, int ld_dense, long long total,
-                                             int row, int ff, int experts) {
+// ---------------------------------------------------------------------------------------
+// The experts' products over the chosen (token, expert) pairs only. The pairs are sorted by
+// expert into rows of a staging matrix, every expert's rows padded to whole tiles of `tile`
+// rows, so that a tile of the grouped product reads one expert's weights:
+//
+//   rank[i]        the pair's place among its expert's rows (any order: a row's product does not
+//                  depend on where in a tile it lies), -1 for an expert without tensors
+//   first[e]       the expert's first row; tiles[2 j], tiles[2 j + 1]: tile j's expert (-1: unused)
+//                  and how many of its rows are pairs
+//   rows[i]        the pair's row, -1 for an expert without tensors
+// ---------------------------------------------------------------------------------------
+__global__ void expert_rank_kernel(int* __restrict__ rank, int* __restrict__ counts, const int* __restrict__ chosen, int pairs,
+                                   int experts) {
   dependent_launch_prologue();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const long long t = i / row;
-  const int c = (int)(i - t * row), e = c / ff;
-  if (e >= experts) return;
-  h[i] = from_float<T>(to_float(h[i]) * dense[t * ld_dense + e]);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pairs) return;
+  const int e = chosen[i];
+  rank[i] = (e >= 0 && e < experts) ? atomicAdd(counts + e, 1) : -1;
 }
 
-// out[t, :] = x[t, :] * sum of dense[t, first .. first + count) (+ residual[t, :]): the share of the
-// experts that return their input, with what the product after it is to add anyway.
+__global__ void __launch_bounds__(256) expert_tiles_kernel(int* __restrict__ first, int* __restrict__ tiles,
+                                                            const int* __restrict__ counts, int experts, int tile, int max_tiles) {
+  dependent_launch_prologue();
+  if (threadIdx.x == 0) {
+    int at = 0;                                         // in tiles
+    for (int e = 0; e < experts; ++e) {
+      first[e] = at * tile;
+      at += (counts[e] + tile - 1) / tile;
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < max_tiles; j += blockDim.x) {
+    tiles[2 * j] = -1;
+    tiles[2 * j + 1] = 0;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int n = counts[e], t0 = first[e] / tile;
+    for (int j = 0; j * tile < n && t0 + j < max_tiles; ++j) {
+      tiles[2 * (t0 + j)] = e;
+      tiles[2 * (t0 + j) + 1] = min(tile, n - j * tile);
+    }
+  }
+}
+
+// One block per pair: its row is its expert's first row plus its rank; the token's input goes there.
 template <typename T>
-__global__ void identity_share_kernel(float* __restrict__ out, const T* __restrict__ x, const float* __restrict__ dense,
-                                      const float* __restrict__ residual, int ld_dense, int first, int count, long long total,
-                                      int width) {
+__global__ void __launch_bounds__(128) expert_gather_kernel(T* __restrict__ staged, int* __restrict__ rows, const T* __restrict__ x,
+                                                            const int* __restrict__ chosen, const int* __restrict__ rank,
+                                                            const int* __restrict__ first, int top, int width, int max_rows) {
+  dependent_launch_prologue();
+  const int i = blockIdx.x;
+  const int r = rank[i];
+  int row = -1;
+  if (r >= 0) {
+    row = first[chosen[i]] + r;
+    if (row >= max_rows) row = -1;                      // cannot happen with the bound the caller computes
+  }
+  if (threadIdx.x == 0) rows[i] = row;
+  if (row < 0) return;
+  const T* src = x + (size_t)(i / top) * width;
+  T* dst = staged + (size_t)row * width;
+  if (((sizeof(T) * width) & 15) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+    const int n = (int)(sizeof(T) * width / 16);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) ((int4*)dst)[c] = ((const int4*)src)[c];
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+  }
+}
+
+// out[t, :] = (base[t, :]) + sum over the token's chosen experts k, in the order of the choice, of
+// weights[t, k] * (y[rows[t, k], :] for an expert with tensors, x[t, :] for one that returns its input).
+template <typename T>
+__global__ void expert_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ rows,
+                                      const float* __restrict__ weights, const T* __restrict__ x, const float* __restrict__ base,
+                                      int top, int width, long long total) {
   dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const float* w = dense + (i / width) * ld_dense + first;
-  float sum = 0.f;
-  for (int k = 0; k < count; ++k) sum += w[k];
-  const float v = to_float(x[i]) * sum;
-  out[i] = residual != nullptr ? v + residual[i] : v;
+  const long long t = i / width;
+  const int c = (int)(i - t * width);
+  float acc = base != nullptr ? base[i] : 0.f;
+  for (int k = 0; k < top; ++k) {
+    const int row = rows[t * top + k];
+    const float w = weights[t * top + k];
+    acc += w * (row >= 0 ? y[(size_t)row * width + c] : to_float(x[i]));
+  }
+  out[i] = acc;
 }
 
 }  // namespace
@@ -183,30 +243,46 @@ PAE_EXPORT int pae_route(int* chosen, float* weights, float* dense, const float*
   return check_launch("route");
 }
 
-PAE_EXPORT int pae_weight_expert_columns(void* h, const float* dense, int ld_dense, int tokens, int row, int ff, int experts,
-                                         int dtype, void* stream) {
-  const long long total = (long long)tokens * row;
-  if (total == 0 || experts == 0) return 0;
-  if (ff < 1 || (long long)experts * ff > row || experts > ld_dense) return fail(2, "weight_expert_columns: %d experts of %d columns in rows of %d", experts, ff, row);
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == kF32) launch_kernel(weight_expert_columns_kernel<float>, blocks, 256, 0, s, (float*)h, dense, ld_dense, total, row, ff, experts);
-  else if (dtype == kBF16) launch_kernel(weight_expert_columns_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)h, dense, ld_dense, total, row, ff, experts);
-  else return fail(1, "weight_expert_columns: unknown dtype %d", dtype);
-  return check_launch("weight_expert_columns");
+// How many tiles of `tile` rows the pairs of `pairs` (token, expert) choices among `experts`
+// experts can need at most: every expert that has a pair may leave one tile partly filled.
+PAE_EXPORT int pae_expert_max_tiles(int pairs, int experts, int tile) {
+  return (pairs < experts ? pairs : experts) + pairs / tile;
 }
 
-PAE_EXPORT int pae_identity_share(float* out, const void* x, const float* dense, const float* residual, int ld_dense, int first, int count, int tokens,
-                                  int width, int dtype, void* stream) {
+// Sorts the pairs chosen [tokens, top] by expert (see above). scratch: int32 [experts] counts, then
+// [experts] first rows, then [tokens * top] ranks. tiles: int32 [max_tiles, 2]; rows: int32
+// [tokens, top]; staged [max_tiles * tile, width] receives the tokens' inputs x [tokens, width].
+PAE_EXPORT int pae_expert_plan(int* scratch, int* tiles, int* rows, void* staged, const void* x, const int* chosen, int tokens,
+                               int top, int experts, int tile, int max_tiles, int width, int dtype, void* stream) {
+  const int pairs = tokens * top;
+  if (pairs == 0) return 0;
+  if (experts < 1 || tile < 1 || max_tiles < pae_expert_max_tiles(pairs, experts, tile))
+    return fail(2, "expert_plan: %d tiles of %d rows for %d pairs over %d experts", max_tiles, tile, pairs, experts);
+  cudaStream_t s = (cudaStream_t)stream;
+  int *counts = scratch, *first = scratch + experts, *rank = scratch + 2 * experts;
+  cudaError_t err = cudaMemsetAsync(counts, 0, sizeof(int) * experts, s);
+  if (err != cudaSuccess) return fail(100, "expert_plan: %s", cudaGetErrorString(err));
+  launch_kernel(expert_rank_kernel, (pairs + 255) / 256, 256, 0, s, rank, counts, chosen, pairs, experts);
+  launch_kernel(expert_tiles_kernel, 1, 256, 0, s, first, tiles, (const int*)counts, experts, tile, max_tiles);
+  const int max_rows = max_tiles * tile;
+  if (dtype == kF32)
+    launch_kernel(expert_gather_kernel<float>, pairs, 128, 0, s, (float*)staged, rows, (const float*)x, chosen, (const int*)rank, (const int*)first, top, width, max_rows);
+  else if (dtype == kBF16)
+    launch_kernel(expert_gather_kernel<__nv_bfloat16>, pairs, 128, 0, s, (__nv_bfloat16*)staged, rows, (const __nv_bfloat16*)x, chosen, (const int*)rank, (const int*)first, top, width, max_rows);
+  else return fail(1, "expert_plan: unknown dtype %d", dtype);
+  return check_launch("expert_plan");
+}
+
+PAE_EXPORT int pae_expert_combine(float* out, const float* y, const int* rows, const float* weights, const void* x, const float* base,
+                                  int tokens, int top, int width, int dtype, void* stream) {
   const long long total = (long long)tokens * width;
   if (total == 0) return 0;
-  if (first < 0 || count < 1 || first + count > ld_dense) return fail(2, "identity_share: experts %d..%d of %d", first, first + count, ld_dense);
   const unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == kF32) launch_kernel(identity_share_kernel<float>, blocks, 256, 0, s, out, (const float*)x, dense, residual, ld_dense, first, count, total, width);
-  else if (dtype == kBF16) launch_kernel(identity_share_kernel<__nv_bfloat16>, blocks, 256, 0, s, out, (const __nv_bfloat16*)x, dense, residual, ld_dense, first, count, total, width);
-  else return fail(1, "identity_share: unknown dtype %d", dtype);
-  return check_launch("identity_share");
+  if (dtype == kF32) launch_kernel(expert_combine_kernel<float>, blocks, 256, 0, s, out, y, rows, weights, (const float*)x, base, top, width, total);
+  else if (dtype == kBF16) launch_kernel(expert_combine_kernel<__nv_bfloat16>, blocks, 256, 0, s, out, y, rows, weights, (const __nv_bfloat16*)x, base, top, width, total);
+  else return fail(1, "expert_combine: unknown dtype %d", dtype);
+  return check_launch("expert_combine");
 }
 
 PAE_DEFINE_LAST_ERROR()

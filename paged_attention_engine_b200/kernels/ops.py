@@ -1392,12 +1392,12 @@ def streams_read_norm(x, in_w, norm_w: torch.Tensor, eps: float, streams: int, o
 
 
 def route(logits, correction, top: int, groups: int = 0, keep: int = 0, score: str = "softmax", eps: float = 0.0,
-          scale: float = 1.0):
+          scale: float = 1.0, dense: bool = True):
     """Chooses `top` experts per token from float32 router logits [tokens, experts] (csrc/routing.cu):
     scores softmax (or sigmoid) of the logits, the choice by score + correction among the experts of
     the `keep` best of `groups` groups (0: all experts), weights score / (sum of the chosen + eps) *
     scale. -> (chosen int32 [tokens, top], weights float32 [tokens, top], dense float32 [tokens,
-    experts] with the weights at the chosen experts' columns and 0 elsewhere)."""
+    experts] with the weights at the chosen experts' columns and 0 elsewhere, or None when `dense` is False)."""
     logits = materialized(logits)
     _need(logits, "route: logits", torch.float32)
     tokens, total = logits.shape
@@ -1409,35 +1409,86 @@ def route(logits, correction, top: int, groups: int = 0, keep: int = 0, score: s
         raise KernelError(f"route: score '{score}' (softmax, sigmoid)")
     chosen = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
-    dense = torch.empty((tokens, total), dtype=torch.float32, device=logits.device)
+    dense = torch.empty((tokens, total), dtype=torch.float32, device=logits.device) if dense else None
     lib = _lib("routing")
     _check(lib, lib.pae_route(_ptr(chosen), _ptr(weights), _ptr(dense), _ptr(logits), _ptr(correction), tokens, total, top,
                               groups, keep, 1 if score == "sigmoid" else 0, float(eps), float(scale), _stream()))
     return chosen, weights, dense
 
 
-def weight_expert_columns(hidden, dense, ff: int, experts: int) -> torch.Tensor:
-    """hidden[t, e * ff + j] *= dense[t, e] for e < experts, in place; further columns stay."""
-    hidden = materialized(hidden)
-    _need(hidden, "weight_expert_columns: hidden")
-    _need(dense, "weight_expert_columns: weights", torch.float32)
-    lib = _lib("routing")
-    _check(lib, lib.pae_weight_expert_columns(_ptr(hidden), _ptr(dense), dense.shape[1], hidden.shape[0], hidden.shape[1], ff,
-                                              experts, _code(hidden), _stream()))
-    return hidden
+EXPERT_TILE = 128
 
 
-def identity_share(x, dense, first: int, count: int, residual=None) -> torch.Tensor:
-    """float32 x[t, :] * sum(dense[t, first : first + count]) (+ a float32 residual): what experts that
-    return their input add."""
+class ExpertPlan:
+    """The (token, expert) pairs of a step sorted by expert: `staged` [max_tiles * tile, width] holds
+    the tokens' inputs in rows grouped by expert and padded to whole tiles, `tiles` int32 [max_tiles,
+    2] each tile's expert (negative: unused) and how many of its rows are pairs, `rows` int32
+    [tokens, top] each pair's row (negative: an expert without tensors)."""
+
+    def __init__(self, staged, tiles, rows, experts: int) -> None:
+        self.staged, self.tiles, self.rows, self.experts = staged, tiles, rows, experts
+
+
+def expert_plan(x, chosen, experts: int) -> ExpertPlan:
+    """Sorts the pairs of `chosen` int32 [tokens, top] by expert and copies every pair's input row
+    of x [tokens, width] into the staging matrix (csrc/routing.cu). Experts from `experts` on have no
+    tensors and get no rows. Every shape depends on (tokens, top, experts) alone, so a replayed step
+    keeps its buffers."""
     x = materialized(x)
-    residual = materialized(residual)
-    _need(x, "identity_share: x")
-    if residual is not None:
-        _need(residual, "identity_share: residual", torch.float32)
-    _need(dense, "identity_share: weights", torch.float32)
+    _need(x, "expert_plan: x")
+    _need(chosen, "expert_plan: chosen", torch.int32)
+    tokens, top = chosen.shape
+    lib = _lib("routing")
+    max_tiles = lib.pae_expert_max_tiles(tokens * top, experts, EXPERT_TILE)
+    staged = torch.empty((max_tiles * EXPERT_TILE, x.shape[1]), dtype=x.dtype, device=x.device)
+    tiles = torch.empty((max_tiles, 2), dtype=torch.int32, device=x.device)
+    rows = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    scratch = torch.empty((2 * experts + tokens * top,), dtype=torch.int32, device=x.device)
+    _check(lib, lib.pae_expert_plan(_ptr(scratch), _ptr(tiles), _ptr(rows), _ptr(staged), _ptr(x), _ptr(chosen), tokens, top, experts,
+                                    EXPERT_TILE, max_tiles, x.shape[1], _code(x), _stream()), 4)
+    return ExpertPlan(staged, tiles, rows, experts)
+
+
+def linear_grouped(x, weight, plan: ExpertPlan, out_dtype=None, activation: str | None = None) -> torch.Tensor:
+    """out[row] = act(x[row] . weight[g(row)]^T) for the rows of the plan's tiles: x [max_tiles *
+    tile, K] sorted by expert, weight [experts, N, K]. Rows that are no pair keep what the fresh
+    output held. The tcgen05 kernel walks the tiles as it walks a plain product's (bfloat16, K a
+    multiple of 8); everything else, float32 above all, takes the CUDA-core kernel."""
+    _need(x, "linear_grouped: x")
+    _need(weight, "linear_grouped: weight", x.dtype)
+    experts, n, k = weight.shape
+    if x.shape[1] != k or experts != plan.experts or x.shape[0] != plan.tiles.shape[0] * EXPERT_TILE:
+        raise KernelError(f"linear_grouped: x {tuple(x.shape)}, weight {tuple(weight.shape)}, {plan.tiles.shape[0]} tiles of {plan.experts} experts")
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
+    max_tiles = plan.tiles.shape[0]
+    if _tensor_core_shape(x, weight, None, out_dtype):
+        lib = _lib("gemm_tcgen05")
+        _check(lib, lib.pae_linear_grouped_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(plan.tiles), max_tiles, experts, n, k,
+                                                   1 if out_dtype == torch.float32 else 0, ACTIVATIONS[activation],
+                                                   _ptr(_error_flag(x.device)), _stream()))
+        return out
+    lib = _lib("gemm_simt")
+    _check(lib, lib.pae_linear_grouped_simt(_ptr(out), _ptr(x), _ptr(weight), _ptr(plan.tiles), max_tiles, EXPERT_TILE, n, k,
+                                            _code(x), _DTYPE_CODE[out_dtype], ACTIVATIONS[activation], _stream()))
+    return out
+
+
+def expert_combine(y, plan: ExpertPlan, weights, x, base=None) -> torch.Tensor:
+    """float32 out[t] = (base[t]) + sum over the token's chosen experts, in the order of the choice, of
+    weights[t, k] * (y[rows[t, k]] for an expert with tensors, x[t] for one that returns its input).
+    y float32 [rows, width] (or None when no expert has tensors), x [tokens, width], base float32."""
+    x = materialized(x)
+    base = materialized(base)
+    _need(x, "expert_combine: x")
+    _need(weights, "expert_combine: weights", torch.float32)
+    if y is not None:
+        _need(y, "expert_combine: y", torch.float32)
+    if base is not None:
+        _need(base, "expert_combine: base", torch.float32)
     out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
     lib = _lib("routing")
-    _check(lib, lib.pae_identity_share(_ptr(out), _ptr(x), _ptr(dense), _ptr(residual), dense.shape[1], first, count, x.shape[0], x.shape[1],
-                                       _code(x), _stream()))
+    _check(lib, lib.pae_expert_combine(_ptr(out), _ptr(y), _ptr(plan.rows), _ptr(weights), _ptr(x), _ptr(base), x.shape[0],
+                                       weights.shape[1], x.shape[1], _code(x), _stream()))
     return out
+

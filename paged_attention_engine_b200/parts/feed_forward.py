@@ -125,11 +125,12 @@ class RoutedExperts(Part):
     tensors: router [num_experts + identity_experts, hidden], correction (the same count),
     e<i>.up [intermediate, hidden], e<i>.down [hidden, intermediate], shared.up, shared.down.
 
-    The experts run as two products over all tokens: every expert's up projection (and the shared
-    expert's) side by side, each expert's hidden columns multiplied by the token's weight for
-    it (0 where it was not chosen), and one down projection over all of them, which therefore
-    adds the chosen experts' outputs, weighted, and the shared expert's. What the identity experts
-    add, x times their weights, enters that product's epilogue with the residual."""
+    Only the chosen (token, expert) pairs are computed: the pairs are sorted by expert into a
+    staging matrix whose rows are padded to whole tiles per expert, a grouped product per projection
+    walks the tiles with each tile's own expert's weights (squared ReLU in the first one's epilogue,
+    float32 out of the second), and one kernel adds every token's weighted rows, in the order of its
+    choice, and its input times the weights of the experts that return their input, to what the
+    shared expert's two plain products left (which carries the residual, if there is one)."""
 
     @classmethod
     def _sizes(cls, spec: PartSpec):
@@ -164,22 +165,33 @@ class RoutedExperts(Part):
         self.correction = tensors.pop(name("correction")) if p.get("choice_correction") else None
         ups = [tensors.pop(name(f"e{e}.up")) for e in range(self.experts)]
         downs = [tensors.pop(name(f"e{e}.down")) for e in range(self.experts)]
-        if self.shared:
-            ups.append(tensors.pop(name("shared.up")))
-            downs.append(tensors.pop(name("shared.down")))
-        self.up_weight = torch.cat(ups, dim=0).contiguous()          # [experts * ff + shared, hidden]
-        self.down_weight = torch.cat(downs, dim=1).contiguous()      # [hidden, experts * ff + shared]
+        self.up_weight = torch.stack(ups, dim=0).contiguous()            # [experts, ff, hidden]
+        self.down_weight = torch.stack(downs, dim=0).contiguous()        # [experts, hidden, ff]
+        self.shared_up = tensors.pop(name("shared.up")) if self.shared else None
+        self.shared_down = tensors.pop(name("shared.down")) if self.shared else None
+
+    def step_weight_bytes(self, num_tokens: int) -> int:
+        """What a step of `num_tokens` tokens reads: the router, the shared expert and the experts it
+        can be expected to choose (every token draws `top` of all experts alike)."""
+        size = self.up_weight.element_size()
+        total = self.experts + self.identity
+        touched = self.experts * (1.0 - (1.0 - min(1.0, self.top / total)) ** max(1, num_tokens))
+        bytes_ = self.router.numel() * self.router.element_size() + 2 * self.shared * self.hidden * size
+        return int(bytes_ + touched * 2 * self.ff * self.hidden * size)
 
     def forward(self, ctx, x, residual):
         ops = self.ops
         x = ops.materialized(x)
         logits = ops.linear(x, self.router, None, None, out_dtype=torch.float32)
-        _, _, dense = ops.route(logits, self.correction, self.top, self.group_count, self.group_keep, self.score,
-                                self.weight_eps, self.weight_scale)
-        hidden = ops.linear(x, self.up_weight, None, activation=self.activation)
-        hidden = ops.weight_expert_columns(hidden, dense, self.ff, self.experts)
-        out_dtype = residual.dtype if residual is not None else torch.float32
-        if self.identity:
-            # float32, as the residual of such a model is
-            residual, out_dtype = ops.identity_share(x, dense, self.experts, self.identity, residual), torch.float32
-        return ops.linear(hidden, self.down_weight, None, residual, out_dtype=out_dtype)
+        chosen, weights, _ = ops.route(logits, self.correction, self.top, self.group_count, self.group_keep, self.score,
+                                       self.weight_eps, self.weight_scale, dense=False)
+        base = ops.materialized(residual)
+        if base is not None and base.dtype != torch.float32:
+            base = residual = base.float()
+        if self.shared:
+            hidden = ops.linear(x, self.shared_up, None, activation=self.activation)
+            base = ops.linear(hidden, self.shared_down, None, residual, out_dtype=torch.float32)
+        plan = ops.expert_plan(x, chosen, self.experts)
+        hidden = ops.linear_grouped(plan.staged, self.up_weight, plan, activation=self.activation)
+        y = ops.linear_grouped(hidden, self.down_weight, plan, out_dtype=torch.float32)
+        return ops.expert_combine(y, plan, weights, x, base)

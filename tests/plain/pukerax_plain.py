@@ -18,9 +18,17 @@ import torch
 
 F = torch.float64
 
+# A function applied to every sublayer's input (the normed read of the stream), or None. Tests set
+# it to a rounding to bfloat16 to learn how far one rounding of an input moves a model's logits.
+narrow = None
+
 
 def _f(t):
     return t.to(F)
+
+
+def _input(h):
+    return narrow(h) if narrow is not None else h
 
 
 def rms_norm(x, weight, eps, offset=0.0):
@@ -32,12 +40,12 @@ def rotate_interleaved(x, positions, dims, base):
     """Turns the pairs (2i, 2i + 1), i < dims / 2, of the last axis of x [T, ..., n] by the angle
     p * base^(-2i / dims); channels from `dims` on pass."""
     out = x.clone()
-    for t, p in enumerate(positions):
-        for i in range(dims // 2):
-            a = p * float(base) ** (-2.0 * i / dims)
-            u, v = x[t, ..., 2 * i], x[t, ..., 2 * i + 1]
-            out[t, ..., 2 * i] = u * math.cos(a) - v * math.sin(a)
-            out[t, ..., 2 * i + 1] = v * math.cos(a) + u * math.sin(a)
+    where = torch.tensor(positions, dtype=F).view(-1, *([1] * (x.dim() - 2)))
+    for i in range(dims // 2):
+        a = where * float(base) ** (-2.0 * i / dims)
+        u, v = x[..., 2 * i], x[..., 2 * i + 1]
+        out[..., 2 * i] = u * torch.cos(a) - v * torch.sin(a)
+        out[..., 2 * i + 1] = v * torch.cos(a) + u * torch.sin(a)
     return out
 
 
@@ -78,37 +86,57 @@ def squared_relu_mlp(h, up, down):
     return (z * z) @ _f(down).T
 
 
-def route(h, router, correction, r):
-    """Per token the chosen experts and their weights: ([T, top] indices, [T, top] weights)."""
+def identity_expert(h):
+    """An expert without tensors: its output is its input."""
+    return h
+
+
+def _gap(values, k):
+    """Per row, how far the k-th largest value is from the next one (infinite when there is none)."""
+    if k >= values.shape[-1]:
+        return torch.full(values.shape[:-1], math.inf, dtype=F)
+    top = values.topk(k + 1, dim=-1).values
+    return top[..., k - 1] - top[..., k]
+
+
+def route(h, router, correction, r, margins=None):
+    """Per token the chosen experts and their weights: ([T, top] indices, [T, top] weights).
+    `margins`, a list, receives per token how close the choice was: the smaller of the gaps
+    between the last kept and the first dropped group, and the last chosen and the first
+    unchosen expert."""
     total = router.shape[0]
     scores = torch.softmax(h @ _f(router).T, dim=-1)                    # [T, E + I]
     choice = scores + _f(correction)
     groups = r.get("groups")
+    margin = torch.full((h.shape[0],), math.inf, dtype=F)
     if groups:
         size = total // groups["count"]
         best = choice.view(-1, groups["count"], size).max(dim=-1).values
+        margin = _gap(best, groups["keep"])
         kept = best.topk(groups["keep"], dim=-1).indices
         allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
         choice = choice.masked_fill(~allowed.repeat_interleave(size, dim=1), -math.inf)
     chosen = choice.topk(r["top"], dim=-1).indices
+    if margins is not None:
+        margins.append(torch.minimum(margin, _gap(choice, r["top"])))
     weights = scores.gather(1, chosen)
     weights = weights / (weights.sum(dim=-1, keepdim=True) + 1e-20) * r["scale"]
     return chosen, weights
 
 
-def routed_feed_forward(h, tensors, prefix, mlp):
+def routed_feed_forward(h, tensors, prefix, mlp, margins=None):
     r = mlp["router"]
     identity = int(r.get("identity") or 0)
     real = r["experts"]
     correction = tensors.get(f"{prefix}.correction")
     if correction is None:
         correction = torch.zeros(real + identity)
-    chosen, weights = route(h, tensors[f"{prefix}.router"], correction, r)
+    chosen, weights = route(h, tensors[f"{prefix}.router"], correction, r, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, w in zip(chosen[t].tolist(), weights[t]):
             if e >= real:
-                out[t] += w * h[t]
+                out[t] += w * identity_expert(h[t])
             else:
                 out[t] += w * squared_relu_mlp(h[t : t + 1], tensors[f"{prefix}.e{e}.up"], tensors[f"{prefix}.e{e}.down"])[0]
     if mlp.get("shared"):
@@ -116,10 +144,10 @@ def routed_feed_forward(h, tensors, prefix, mlp):
     return out
 
 
-def feed_forward(h, tensors, prefix, mlp):
+def feed_forward(h, tensors, prefix, mlp, margins=None):
     if mlp["kind"] == "dense":
         return squared_relu_mlp(h, tensors[f"{prefix}.up"], tensors[f"{prefix}.down"])
-    return routed_feed_forward(h, tensors, prefix, mlp)
+    return routed_feed_forward(h, tensors, prefix, mlp, margins)
 
 
 def connect(streams, y, tensors, prefix):
@@ -128,9 +156,10 @@ def connect(streams, y, tensors, prefix):
     return torch.einsum("st,snw->tnw", mix, streams) + out[:, None, None] * y[None]
 
 
-def forward(raw, tensors, tokens, layer_outputs=None):
+def forward(raw, tensors, tokens, layer_outputs=None, margins=None):
     """float64 logits [T, vocab] of one sequence; `layer_outputs`, a list, receives the residual
-    stream (the sum of the streams) after every layer."""
+    stream (the sum of the streams) after every layer, `margins`, a list, per routed layer how
+    close every token's choice of experts was."""
     eps = raw["norm"]["eps"]
     positions = list(range(len(tokens)))
     x = _f(tensors["embed"])[torch.tensor(tokens, dtype=torch.long)]
@@ -139,13 +168,13 @@ def forward(raw, tensors, tokens, layer_outputs=None):
     for i, layer in enumerate(raw["layers"]):
         branches = [(1, lambda h: latent_attention(h, tensors, f"l{i}.mix", layer["mixer"], eps, positions))]
         if layer.get("mlp"):
-            branches.append((2, lambda h: feed_forward(h, tensors, f"l{i}.mlp", layer["mlp"])))
+            branches.append((2, lambda h: feed_forward(h, tensors, f"l{i}.mlp", layer["mlp"], margins)))
         for q, branch in branches:
             if S:
                 u = torch.einsum("s,snw->nw", _f(tensors[f"l{i}.hc{q}.in"]), streams)
-                streams = connect(streams, branch(rms_norm(u, tensors[f"l{i}.norm{q}"], eps, 1.0)), tensors, f"l{i}.hc{q}")
+                streams = connect(streams, branch(_input(rms_norm(u, tensors[f"l{i}.norm{q}"], eps, 1.0))), tensors, f"l{i}.hc{q}")
             else:
-                x = x + branch(rms_norm(x, tensors[f"l{i}.norm{q}"], eps, 1.0))
+                x = x + branch(_input(rms_norm(x, tensors[f"l{i}.norm{q}"], eps, 1.0)))
         if layer_outputs is not None:
             layer_outputs.append(streams.sum(dim=0) if S else x)
     if S:
