@@ -39,6 +39,8 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
+// PER_LANE: experts per lane, 32 * PER_LANE >= total.
+template <int PER_LANE>
 __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
   dependent_launch_prologue();
   extern __shared__ float shared[];                    // per warp: choice [total], group score [groups]
@@ -48,33 +50,33 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
   float* choice = shared + (size_t)warp * (p.total + p.groups);
   float* group_score = choice + p.total;
   const float* z = p.logits + (size_t)t * p.total;
-  float s[MAX_PER_LANE];
+  float s[PER_LANE];
   float top = -FLT_MAX;
 #pragma unroll
-  for (int j = 0; j < MAX_PER_LANE; ++j) {
+  for (int j = 0; j < PER_LANE; ++j) {
     const int e = lane + 32 * j;
     s[j] = e < p.total ? z[e] : -FLT_MAX;
     top = fmaxf(top, s[j]);
   }
   if (p.sigmoid) {
 #pragma unroll
-    for (int j = 0; j < MAX_PER_LANE; ++j) s[j] = lane + 32 * j < p.total ? 1.f / (1.f + expf(-s[j])) : 0.f;
+    for (int j = 0; j < PER_LANE; ++j) s[j] = lane + 32 * j < p.total ? 1.f / (1.f + expf(-s[j])) : 0.f;
   } else {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
     float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < MAX_PER_LANE; ++j) {
+    for (int j = 0; j < PER_LANE; ++j) {
       s[j] = lane + 32 * j < p.total ? expf(s[j] - top) : 0.f;
       sum += s[j];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
 #pragma unroll
-    for (int j = 0; j < MAX_PER_LANE; ++j) s[j] = s[j] / sum;
+    for (int j = 0; j < PER_LANE; ++j) s[j] = s[j] / sum;
   }
 #pragma unroll
-  for (int j = 0; j < MAX_PER_LANE; ++j) {
+  for (int j = 0; j < PER_LANE; ++j) {
     const int e = lane + 32 * j;
     if (e < p.total) {
       choice[e] = s[j] + (p.correction != nullptr ? p.correction[e] : 0.f);
@@ -110,7 +112,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
     float v = -INFINITY;
     int i = INT_MAX;
 #pragma unroll
-    for (int j = 0; j < MAX_PER_LANE; ++j) {
+    for (int j = 0; j < PER_LANE; ++j) {
       const int e = lane + 32 * j;
       if (e < p.total && !((mine >> j) & 1) && (i == INT_MAX || choice[e] > v)) { v = choice[e]; i = e; }
     }
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
     if (i != INT_MAX && (i & 31) == lane) {
       mine |= 1 << (i >> 5);
 #pragma unroll
-      for (int j = 0; j < MAX_PER_LANE; ++j)
+      for (int j = 0; j < PER_LANE; ++j)
         if (j == (i >> 5)) score = s[j];
     }
     score = __shfl_sync(0xffffffffu, score, i == INT_MAX ? 0 : (i & 31));
@@ -208,6 +210,75 @@ __global__ void __launch_bounds__(128) expert_gather_kernel(T* __restrict__ stag
   }
 }
 
+// The same three steps for a step of few pairs (decoding) in ONE block: counts, first rows and rows
+// live in shared memory, a warp copies a pair's input row.
+constexpr int SMALL_PAIRS = 2048, SMALL_THREADS = 1024;
+
+template <typename T>
+__global__ void __launch_bounds__(SMALL_THREADS) expert_plan_small_kernel(int* __restrict__ tiles, int* __restrict__ rows,
+                                                                          T* __restrict__ staged, const T* __restrict__ x,
+                                                                          const int* __restrict__ chosen, int pairs, int top,
+                                                                          int experts, int tile, int max_tiles, int width) {
+  dependent_launch_prologue();
+  __shared__ int counts[32 * MAX_PER_LANE], first[32 * MAX_PER_LANE], row_of[SMALL_PAIRS];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  for (int j = threadIdx.x; j < max_tiles; j += blockDim.x) {
+    tiles[2 * j] = -1;
+    tiles[2 * j + 1] = 0;
+  }
+  __syncthreads();
+  int rank[SMALL_PAIRS / SMALL_THREADS];
+#pragma unroll
+  for (int n = 0; n < SMALL_PAIRS / SMALL_THREADS; ++n) {
+    const int i = threadIdx.x + n * SMALL_THREADS;
+    rank[n] = -1;
+    if (i < pairs) {
+      const int e = chosen[i];
+      if (e >= 0 && e < experts) rank[n] = atomicAdd(counts + e, 1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < experts; ++e) {
+      first[e] = at * tile;
+      at += (counts[e] + tile - 1) / tile;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int n = counts[e], t0 = first[e] / tile;
+    for (int j = 0; j * tile < n && t0 + j < max_tiles; ++j) {
+      tiles[2 * (t0 + j)] = e;
+      tiles[2 * (t0 + j) + 1] = min(tile, n - j * tile);
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < SMALL_PAIRS / SMALL_THREADS; ++n) {
+    const int i = threadIdx.x + n * SMALL_THREADS;
+    if (i < pairs) {
+      int row = rank[n] >= 0 ? first[chosen[i]] + rank[n] : -1;
+      if (row >= max_tiles * tile) row = -1;
+      row_of[i] = row;
+      rows[i] = row;
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = warp; i < pairs; i += SMALL_THREADS / 32) {
+    const int row = row_of[i];
+    if (row < 0) continue;
+    const T* src = x + (size_t)(i / top) * width;
+    T* dst = staged + (size_t)row * width;
+    if (((sizeof(T) * width) & 15) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+      const int n16 = (int)(sizeof(T) * width / 16);
+      for (int c = lane; c < n16; c += 32) ((int4*)dst)[c] = ((const int4*)src)[c];
+    } else {
+      for (int c = lane; c < width; c += 32) dst[c] = src[c];
+    }
+  }
+}
+
 // out[t, :] = (base[t, :]) + sum over the token's chosen experts k, in the order of the choice, of
 // weights[t, k] * (y[rows[t, k], :] for an expert with tensors, x[t, :] for one that returns its input).
 template <typename T>
@@ -239,7 +310,13 @@ PAE_EXPORT int pae_route(int* chosen, float* weights, float* dense, const float*
     return fail(2, "route: %d experts in %d groups of which %d are kept, %d chosen", total, groups, keep, top);
   Route p{logits, correction, chosen, weights, dense, tokens, total, top, groups, keep, sigmoid, eps, scale};
   const size_t smem = sizeof(float) * WARPS * (size_t)(total + groups);
-  launch_kernel(route_kernel, (tokens + WARPS - 1) / WARPS, WARPS * 32, smem, (cudaStream_t)stream, p);
+  const unsigned blocks = (tokens + WARPS - 1) / WARPS;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (total <= 32) launch_kernel(route_kernel<1>, blocks, WARPS * 32, smem, s, p);
+  else if (total <= 64) launch_kernel(route_kernel<2>, blocks, WARPS * 32, smem, s, p);
+  else if (total <= 128) launch_kernel(route_kernel<4>, blocks, WARPS * 32, smem, s, p);
+  else if (total <= 256) launch_kernel(route_kernel<8>, blocks, WARPS * 32, smem, s, p);
+  else launch_kernel(route_kernel<MAX_PER_LANE>, blocks, WARPS * 32, smem, s, p);
   return check_launch("route");
 }
 
@@ -259,6 +336,14 @@ PAE_EXPORT int pae_expert_plan(int* scratch, int* tiles, int* rows, void* staged
   if (experts < 1 || tile < 1 || max_tiles < pae_expert_max_tiles(pairs, experts, tile))
     return fail(2, "expert_plan: %d tiles of %d rows for %d pairs over %d experts", max_tiles, tile, pairs, experts);
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype != kF32 && dtype != kBF16) return fail(1, "expert_plan: unknown dtype %d", dtype);
+  if (pairs <= SMALL_PAIRS && experts <= 32 * MAX_PER_LANE) {
+    if (dtype == kF32)
+      launch_kernel(expert_plan_small_kernel<float>, 1, SMALL_THREADS, 0, s, tiles, rows, (float*)staged, (const float*)x, chosen, pairs, top, experts, tile, max_tiles, width);
+    else
+      launch_kernel(expert_plan_small_kernel<__nv_bfloat16>, 1, SMALL_THREADS, 0, s, tiles, rows, (__nv_bfloat16*)staged, (const __nv_bfloat16*)x, chosen, pairs, top, experts, tile, max_tiles, width);
+    return check_launch("expert_plan");
+  }
   int *counts = scratch, *first = scratch + experts, *rank = scratch + 2 * experts;
   cudaError_t err = cudaMemsetAsync(counts, 0, sizeof(int) * experts, s);
   if (err != cudaSuccess) return fail(100, "expert_plan: %s", cudaGetErrorString(err));

@@ -18,8 +18,9 @@ using namespace pae;
 
 namespace {
 
-constexpr int MAX_STREAMS = 8;
-constexpr int THREADS = 256;
+constexpr int MAX_STREAMS = 16;       // S * S mixing weights are loaded by the block's 256 threads
+constexpr int THREADS = 256;            // a block of a step of many tokens
+constexpr int MAX_THREADS = 1024;       // ... of few tokens: a block per token, so the columns are spread over more threads
 
 struct StreamsStep {
   const float* x;        // [tokens, src_streams, width]
@@ -70,9 +71,9 @@ __device__ __forceinline__ void column(const StreamsStep& p, const float* mix, c
 }
 
 template <int S, typename TO>
-__global__ void __launch_bounds__(THREADS) streams_step_kernel(const StreamsStep p) {
+__global__ void __launch_bounds__(MAX_THREADS) streams_step_kernel(const StreamsStep p) {
   dependent_launch_prologue();
-  __shared__ double scratch[THREADS / 32];
+  __shared__ double scratch[MAX_THREADS / 32];
   __shared__ float mix[S * S], out_w[S], in_w[S];
   if (threadIdx.x < S * S) mix[threadIdx.x] = p.mix != nullptr ? p.mix[threadIdx.x] : 0.f;
   if (threadIdx.x < S) {
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(THREADS) streams_step_kernel(const StreamsStep
   __syncthreads();
   const size_t t = blockIdx.x;
   double squares = 0.0;
-  for (int c = threadIdx.x; c < p.width; c += THREADS) {
+  for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
     float now[S];
     column<S>(p, mix, out_w, t, c, now);
     if (p.x_new != nullptr) {
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(THREADS) streams_step_kernel(const StreamsStep
   if (p.normed == nullptr) return;
   const float inv = (float)(1.0 / sqrt(block_sum(squares, scratch) / (double)p.width + (double)p.eps));
   TO* to = (TO*)p.normed + t * p.width;
-  for (int c = threadIdx.x; c < p.width; c += THREADS) {
+  for (int c = threadIdx.x; c < p.width; c += blockDim.x) {
     float now[S];
     column<S>(p, mix, out_w, t, c, now);       // the same instructions as above: the same bits
     float u = 0.f;
@@ -109,8 +110,13 @@ __global__ void __launch_bounds__(THREADS) streams_step_kernel(const StreamsStep
 
 template <int S>
 int launch_streams(const StreamsStep& p, int tokens, int out_dtype, cudaStream_t s) {
-  if (out_dtype == kF32) launch_kernel(streams_step_kernel<S, float>, tokens, THREADS, 0, s, p);
-  else launch_kernel(streams_step_kernel<S, __nv_bfloat16>, tokens, THREADS, 0, s, p);
+  // Few tokens leave most SMs idle: their blocks take a thread per column (up to 1,024), so that a
+  // token's row is one or two rounds of loads instead of many. The order in which the double sum of
+  // squares is added differs between the two block sizes, by less than float32 resolves.
+  int threads = THREADS;
+  if (tokens <= 256) threads = p.width >= MAX_THREADS ? MAX_THREADS : p.width > THREADS ? (p.width + 31) / 32 * 32 : THREADS;
+  if (out_dtype == kF32) launch_kernel(streams_step_kernel<S, float>, tokens, threads, 0, s, p);
+  else launch_kernel(streams_step_kernel<S, __nv_bfloat16>, tokens, threads, 0, s, p);
   return check_launch("streams_step");
 }
 
@@ -142,7 +148,15 @@ PAE_EXPORT int pae_streams_step(float* x_new, void* normed, const float* x, int 
     case 5: return launch_streams<5>(p, tokens, out_dtype, s);
     case 6: return launch_streams<6>(p, tokens, out_dtype, s);
     case 7: return launch_streams<7>(p, tokens, out_dtype, s);
-    default: return launch_streams<8>(p, tokens, out_dtype, s);
+    case 8: return launch_streams<8>(p, tokens, out_dtype, s);
+    case 9: return launch_streams<9>(p, tokens, out_dtype, s);
+    case 10: return launch_streams<10>(p, tokens, out_dtype, s);
+    case 11: return launch_streams<11>(p, tokens, out_dtype, s);
+    case 12: return launch_streams<12>(p, tokens, out_dtype, s);
+    case 13: return launch_streams<13>(p, tokens, out_dtype, s);
+    case 14: return launch_streams<14>(p, tokens, out_dtype, s);
+    case 15: return launch_streams<15>(p, tokens, out_dtype, s);
+    default: return launch_streams<16>(p, tokens, out_dtype, s);
   }
 }
 
