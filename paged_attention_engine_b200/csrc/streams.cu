@@ -59,8 +59,18 @@ __device__ __forceinline__ void column(const StreamsStep& p, const float* mix, c
     for (int s = 0; s < S; ++s) now[s] = old[s];
     return;
   }
+  // the planes of a split product, added in their order; eight loads are in flight at a time
   float y = 0.f;
-  for (int k = 0; k < p.splits; ++k) y += p.y[k * p.plane + t * p.width + c];
+  const float* plane = p.y + t * p.width + c;
+  int k = 0;
+  for (; k + 8 <= p.splits; k += 8) {
+    float part[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part[i] = plane[(size_t)(k + i) * p.plane];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y += part[i];
+  }
+  for (; k < p.splits; ++k) y += plane[(size_t)k * p.plane];
 #pragma unroll
   for (int to = 0; to < S; ++to) {
     float v = 0.f;
