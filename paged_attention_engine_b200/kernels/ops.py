@@ -1417,6 +1417,8 @@ def route(logits, correction, top: int, groups: int = 0, keep: int = 0, score: s
 
 
 EXPERT_TILE = 128
+# Up to this many pairs one block sorts them (one launch); beyond, a memset and three kernels.
+EXPERT_FEW_PAIRS = 2048
 
 
 class ExpertPlan:
@@ -1445,7 +1447,8 @@ def expert_plan(x, chosen, experts: int) -> ExpertPlan:
     rows = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
     scratch = torch.empty((2 * experts + tokens * top,), dtype=torch.int32, device=x.device)
     _check(lib, lib.pae_expert_plan(_ptr(scratch), _ptr(tiles), _ptr(rows), _ptr(staged), _ptr(x), _ptr(chosen), tokens, top, experts,
-                                    EXPERT_TILE, max_tiles, x.shape[1], _code(x), _stream()), 4)
+                                    EXPERT_TILE, max_tiles, x.shape[1], _code(x), _stream()),
+           1 if tokens * top <= EXPERT_FEW_PAIRS else 4)
     return ExpertPlan(staged, tiles, rows, experts)
 
 
