@@ -318,7 +318,7 @@ def pukerax_config(size: dict, kv_rank: int = 512, rot_dim: int = 64, streams: i
              "scale": (d + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
     dense = {"kind": "dense", "ff": size["ff"]}
     routed = {"kind": "moe", "expert": {"ff": size["ff"] // 8}, "shared": {"ff": size["ff"] // 4},
-              "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+              "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
     layers = [{"type": "latent_attention", "mixer": mixer, "mlp": dense if i == 0 else routed} for i in range(size["layers"])]
     return {"architecture": "Pukerax", "vocab": size["vocab"], "width": size["width"], "streams": streams, "norm": {"eps": 1e-6},
             "layers": json.loads(json.dumps(layers))}

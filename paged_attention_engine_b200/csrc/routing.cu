@@ -21,13 +21,14 @@ constexpr int WARPS = 4;
 constexpr int MAX_PER_LANE = 16;      // 512 experts
 
 struct Route {
-  const float* logits;       // [tokens, total]
+  const float* logits;       // [splits, tokens, total]: the planes of a split product are added in their order
   const float* correction;   // [total] or null
   int* chosen;               // [tokens, top]
   float* weights;            // [tokens, top]
   float* dense;              // [tokens, total] or null
   int tokens, total, top, groups, keep, sigmoid;
   float eps, scale;
+  int splits;
 };
 
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
@@ -55,7 +56,12 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
 #pragma unroll
   for (int j = 0; j < PER_LANE; ++j) {
     const int e = lane + 32 * j;
-    s[j] = e < p.total ? z[e] : -FLT_MAX;
+    s[j] = -FLT_MAX;
+    if (e < p.total) {
+      float sum = z[e];
+      for (int k = 1; k < p.splits; ++k) sum += z[(size_t)k * p.tokens * p.total + e];
+      s[j] = sum;
+    }
     top = fmaxf(top, s[j]);
   }
   if (p.sigmoid) {
@@ -279,18 +285,20 @@ __global__ void __launch_bounds__(SMALL_THREADS) expert_plan_small_kernel(int* _
   }
 }
 
-// out[t, :] = (base[t, :]) + sum over the token's chosen experts k, in the order of the choice, of
+// out[t, :] = (base[t, :], itself the sum of base_planes planes) + sum over the token's chosen experts k, in the order of the choice, of
 // weights[t, k] * (y[rows[t, k], :] for an expert with tensors, x[t, :] for one that returns its input).
 template <typename T>
 __global__ void expert_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ rows,
                                       const float* __restrict__ weights, const T* __restrict__ x, const float* __restrict__ base,
-                                      int top, int width, long long total) {
+                                      int base_planes, int top, int width, long long total) {
   dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long t = i / width;
   const int c = (int)(i - t * width);
-  float acc = base != nullptr ? base[i] : 0.f;
+  float acc = 0.f;                                    // base: the planes of a split product, added in their order
+  if (base != nullptr)
+    for (int k = 0; k < base_planes; ++k) acc += base[(size_t)k * total + i];
   for (int k = 0; k < top; ++k) {
     const int row = rows[t * top + k];
     const float w = weights[t * top + k];
@@ -301,14 +309,15 @@ __global__ void expert_combine_kernel(float* __restrict__ out, const float* __re
 
 }  // namespace
 
-PAE_EXPORT int pae_route(int* chosen, float* weights, float* dense, const float* logits, const float* correction, int tokens,
+PAE_EXPORT int pae_route(int* chosen, float* weights, float* dense, const float* logits, int splits, const float* correction, int tokens,
                          int total, int top, int groups, int keep, int sigmoid, float eps, float scale, void* stream) {
   if (tokens == 0) return 0;
   if (total < 1 || total > 32 * MAX_PER_LANE) return fail(2, "route: %d experts (1 to %d)", total, 32 * MAX_PER_LANE);
   if (top < 1 || top > total) return fail(2, "route: %d of %d experts", top, total);
   if (groups < 0 || (groups > 0 && (total % groups || keep < 1 || keep > groups || top > total / groups * keep)))
     return fail(2, "route: %d experts in %d groups of which %d are kept, %d chosen", total, groups, keep, top);
-  Route p{logits, correction, chosen, weights, dense, tokens, total, top, groups, keep, sigmoid, eps, scale};
+  if (splits < 1) return fail(2, "route: %d planes of logits", splits);
+  Route p{logits, correction, chosen, weights, dense, tokens, total, top, groups, keep, sigmoid, eps, scale, splits};
   const size_t smem = sizeof(float) * WARPS * (size_t)(total + groups);
   const unsigned blocks = (tokens + WARPS - 1) / WARPS;
   cudaStream_t s = (cudaStream_t)stream;
@@ -359,13 +368,13 @@ PAE_EXPORT int pae_expert_plan(int* scratch, int* tiles, int* rows, void* staged
 }
 
 PAE_EXPORT int pae_expert_combine(float* out, const float* y, const int* rows, const float* weights, const void* x, const float* base,
-                                  int tokens, int top, int width, int dtype, void* stream) {
+                                  int base_planes, int tokens, int top, int width, int dtype, void* stream) {
   const long long total = (long long)tokens * width;
   if (total == 0) return 0;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == kF32) launch_kernel(expert_combine_kernel<float>, blocks, 256, 0, s, out, y, rows, weights, (const float*)x, base, top, width, total);
-  else if (dtype == kBF16) launch_kernel(expert_combine_kernel<__nv_bfloat16>, blocks, 256, 0, s, out, y, rows, weights, (const __nv_bfloat16*)x, base, top, width, total);
+  if (dtype == kF32) launch_kernel(expert_combine_kernel<float>, blocks, 256, 0, s, out, y, rows, weights, (const float*)x, base, base_planes, top, width, total);
+  else if (dtype == kBF16) launch_kernel(expert_combine_kernel<__nv_bfloat16>, blocks, 256, 0, s, out, y, rows, weights, (const __nv_bfloat16*)x, base, base_planes, top, width, total);
   else return fail(1, "expert_combine: unknown dtype %d", dtype);
   return check_launch("expert_combine");
 }

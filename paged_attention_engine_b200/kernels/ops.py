@@ -1328,7 +1328,8 @@ def delta_rule(proj, offsets, w_pre, w0, a_bias, gate_offset, norm_weight, state
 def _sublayer_output(y):
     """(float32 planes [splits, tokens, width], splits) of a sublayer's output that is a tensor or a
     split product without bias, residual or activation."""
-    if isinstance(y, PendingSum) and y.value is None and y.bias is None and y.residual is None and not y.activation and fuse_split_sums:
+    if (isinstance(y, PendingSum) and y.value is None and y.bias is None and y.residual is None and not y.activation
+            and y.dtype == torch.float32 and fuse_split_sums):
         return y.partial, int(y.partial.shape[0])
     y = materialized(y)
     _need(y, "streams: the sublayer's output", torch.float32)
@@ -1398,9 +1399,9 @@ def route(logits, correction, top: int, groups: int = 0, keep: int = 0, score: s
     the `keep` best of `groups` groups (0: all experts), weights score / (sum of the chosen + eps) *
     scale. -> (chosen int32 [tokens, top], weights float32 [tokens, top], dense float32 [tokens,
     experts] with the weights at the chosen experts' columns and 0 elsewhere, or None when `dense` is False)."""
-    logits = materialized(logits)
+    logits, splits = _sublayer_output(logits)         # a split product's planes are added by the kernel itself
     _need(logits, "route: logits", torch.float32)
-    tokens, total = logits.shape
+    tokens, total = logits.shape[-2:]
     if correction is not None:
         _need(correction, "route: correction", torch.float32)
         if correction.numel() != total:
@@ -1411,7 +1412,7 @@ def route(logits, correction, top: int, groups: int = 0, keep: int = 0, score: s
     weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
     dense = torch.empty((tokens, total), dtype=torch.float32, device=logits.device) if dense else None
     lib = _lib("routing")
-    _check(lib, lib.pae_route(_ptr(chosen), _ptr(weights), _ptr(dense), _ptr(logits), _ptr(correction), tokens, total, top,
+    _check(lib, lib.pae_route(_ptr(chosen), _ptr(weights), _ptr(dense), _ptr(logits), splits, _ptr(correction), tokens, total, top,
                               groups, keep, 1 if score == "sigmoid" else 0, float(eps), float(scale), _stream()))
     return chosen, weights, dense
 
@@ -1482,7 +1483,9 @@ def expert_combine(y, plan: ExpertPlan, weights, x, base=None) -> torch.Tensor:
     weights[t, k] * (y[rows[t, k]] for an expert with tensors, x[t] for one that returns its input).
     y float32 [rows, width] (or None when no expert has tensors), x [tokens, width], base float32."""
     x = materialized(x)
-    base = materialized(base)
+    planes = 1
+    if base is not None:
+        base, planes = _sublayer_output(base)
     _need(x, "expert_combine: x")
     _need(weights, "expert_combine: weights", torch.float32)
     if y is not None:
@@ -1491,7 +1494,7 @@ def expert_combine(y, plan: ExpertPlan, weights, x, base=None) -> torch.Tensor:
         _need(base, "expert_combine: base", torch.float32)
     out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
     lib = _lib("routing")
-    _check(lib, lib.pae_expert_combine(_ptr(out), _ptr(y), _ptr(plan.rows), _ptr(weights), _ptr(x), _ptr(base), x.shape[0],
+    _check(lib, lib.pae_expert_combine(_ptr(out), _ptr(y), _ptr(plan.rows), _ptr(weights), _ptr(x), _ptr(base), planes, x.shape[0],
                                        weights.shape[1], x.shape[1], _code(x), _stream()))
     return out
 

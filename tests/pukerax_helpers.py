@@ -51,7 +51,7 @@ def config(vocab, width, layers, streams=None, eps=1e-5):
 # chosen experts as one kept group has), groups of one expert each, several kept groups, top 1.
 SMALL_A = config(211, 64, [
     layer(mixer(3, 8, 4, 12, 20, 24, 0.35, base=50000.0), dense(96)),
-    layer(mixer(2, 12, 6, 6, 28, 80, 0.3), moe(40, 6, 2, 2.5, identity=2, groups=(4, 1), shared=24)),
+    layer(mixer(2, 12, 6, 6, 28, 80, 0.3), moe(40, 6, 2, 2.2, identity=2, groups=(4, 1), shared=24)),
     layer(mixer(4, 6, 8, 10, 12, 16, 0.4, base=300.0), None),
     layer(mixer(1, 20, 4, 28, 24, 0, 0.25), moe(56, 5, 3, 1.0)),
     layer(mixer(3, 8, 4, 12, 20, 24, 0.35), moe(24, 9, 1, 0.7, identity=3, groups=(12, 5))),

@@ -75,7 +75,7 @@ def test_streams_read_write_and_both_in_one_kernel(dtype, streams, width, splits
 
 
 @pytest.mark.parametrize("total, top, groups, keep, scale", [
-    (4, 2, 0, 0, 1.0), (10, 2, 2, 1, 2.5), (8, 2, 4, 2, 1.0), (12, 1, 12, 5, 0.7), (16, 4, 4, 2, 3.0), (64, 6, 8, 3, 2.0),
+    (4, 2, 0, 0, 1.0), (10, 3, 2, 1, 1.7), (8, 2, 4, 2, 1.0), (12, 1, 12, 5, 0.7), (16, 4, 4, 2, 3.0), (64, 6, 8, 3, 2.0),
     (40, 8, 0, 0, 1.0), (7, 7, 0, 0, 1.0), (96, 3, 3, 1, 1.0)])
 def test_router_choice_groups_and_weights(total, top, groups, keep, scale):
     ops = _ops()
@@ -98,6 +98,13 @@ def test_router_choice_groups_and_weights(total, top, groups, keep, scale):
     want_dense = torch.zeros(T, total, dtype=torch.float64).scatter_(1, want_chosen, want_weights)
     assert torch.allclose(dense[clear].double(), want_dense[clear], rtol=2e-5, atol=1e-7)
     assert torch.allclose(weights.sum(1), torch.full((T,), scale), rtol=1e-5)
+    # logits that are still the planes of a split product: added in their order by the kernel itself
+    planes = torch.randn(3, T, total, generator=gen)
+    summed = (planes[0] + planes[1]) + planes[2]
+    pending = ops.PendingSum(planes.to(DEV), None, None, torch.float32)
+    one = ops.route(summed.to(DEV), correction.to(DEV), top, groups, keep, "softmax", 1e-20, scale)
+    two = ops.route(pending, correction.to(DEV), top, groups, keep, "softmax", 1e-20, scale)
+    assert pending.value is None and all(torch.equal(a, b) for a, b in zip(one, two))
 
 
 def test_router_without_correction():
@@ -161,6 +168,11 @@ def test_experts_over_the_chosen_pairs_only(dtype, tokens, top, experts, identit
             want[t] += float(weights[t, k]) * (z @ down[e].double().T)
     _close(got, want, dtype, scale=2.0)
     _close(bare, want - base.double(), dtype, scale=2.0)
+    halves = torch.randn(2, tokens, width, generator=gen)
+    pending = ops.PendingSum(halves.to(DEV), None, None, torch.float32)
+    assert torch.equal(ops.expert_combine(y, plan, weights.to(DEV), x.to(DEV), pending),
+                       ops.expert_combine(y, plan, weights.to(DEV), x.to(DEV), (halves[0] + halves[1]).to(DEV)))
+    assert pending.value is None
     ops.check_device_errors()
 
 
