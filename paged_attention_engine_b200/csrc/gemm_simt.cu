@@ -43,8 +43,9 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, co
   if (group_tiles != nullptr) {
     // Grouped: w is one [N, K] matrix per group; the rows of tile j (of `tile` rows, a multiple of BM)
     // multiply matrix group_tiles[2 j], and only the tile's first group_tiles[2 j + 1] rows count.
-    const int j = m0 / tile, g = group_tiles[2 * j];
-    if (g < 0) return;
+    const int j = m0 / tile;
+    if (j >= group_tiles[2 * (M / tile)]) return;          // the table's last entry: how many tiles are in use
+    const int g = group_tiles[2 * j];
     w += (size_t)g * N * K;
     M = min(M, j * tile + group_tiles[2 * j + 1]);
     if (m0 >= M) return;
@@ -134,8 +135,8 @@ PAE_EXPORT int pae_linear_simt(void* out, const void* x, const void* w, const fl
 }
 
 // The grouped product on the CUDA cores: out[row, n] = act(x[row, k] . w[g(row)][n, k]^T) for rows sorted
-// by matrix in tiles of `tile` rows (a multiple of 64); tiles int32 [max_tiles, 2]: each tile's matrix
-// (negative: skipped) and how many of its rows count. x and w of one type (float32: sums in double),
+// by matrix in tiles of `tile` rows (a multiple of 64); tiles int32 [max_tiles + 1, 2]: each tile's matrix
+// and how many of its rows count, and in the last entry how many tiles are in use. x and w of one type (float32: sums in double),
 // out of that type or float32.
 PAE_EXPORT int pae_linear_grouped_simt(void* out, const void* x, const void* w, const int* tiles, int max_tiles, int tile, int n, int k,
                                        int x_dtype, int out_dtype, int activation, void* stream) {

@@ -60,8 +60,9 @@ struct Params {
   __nv_bfloat16* values;
   int heads, kv_heads, head_dim, page_size;
   // Grouped (persistent kernel, NORMAL): the B operand is `groups` matrices of `rows_b` rows one after
-  // another; tile j of the A rows multiplies matrix group_tiles[2 j] (negative: the tile is
-  // skipped) and only its first group_tiles[2 j + 1] rows are stored.
+  // another; tile j of the A rows multiplies matrix group_tiles[2 j] and only its first
+  // group_tiles[2 j + 1] rows are stored; the tiles in use are the first group_tiles[2 tiles] of the
+  // table (the entry after the last tile), the others are skipped.
   const int* group_tiles;
   int groups;
   int* error;
@@ -518,20 +519,30 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
   const int planes = p.planes > 1 ? p.planes : 1;
   const int total_items = tiles_a * tiles_b * planes;
   const int k_blocks = p.k_blocks;
+  // Grouped: how many of the table's tiles are in use, read once by the thread or warp of each role.
+  auto used_tiles = [&]() { return p.group_tiles != nullptr ? min(tiles_a, p.group_tiles[2 * tiles_a]) : tiles_a; };
+  // Which tile of the A rows and which of the B rows a tile index means. Plain: neighbouring
+  // indices (blocks that run at the same time) share the weight tile. Grouped: they share the tile
+  // of the A rows and walk one matrix's weights together, so that the staging rows and every
+  // matrix cross from memory once (the matrices together are the large operand there, and
+  // the blocks of one round would otherwise touch a slice of every one of them).
+  const bool grouped = p.group_tiles != nullptr;
+  auto a_of = [&](int tile) { return grouped ? tile / tiles_b : tile % tiles_a; };
+  auto b_of = [&](int tile) { return grouped ? tile % tiles_b : tile / tiles_a; };
 
   if (warp == 0) {
     if (lane == 0) {
       int it = 0;
       bool ok = true;
+      const int used = used_tiles();
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         const int tile = item / planes, kb_first = (item % planes) * p.kb_per_split;
         const int kb_end = min(kb_first + p.kb_per_split, k_blocks);
-        const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;     // neighbours share the weight tile
+        const int tile_a = a_of(tile), tile_b = b_of(tile);
         int b_row = tile_b * PBN;
         if (p.group_tiles != nullptr) {
-          const int g = p.group_tiles[2 * tile_a];
-          if (g < 0) continue;
-          b_row += g * p.rows_b;
+          if (tile_a >= used) continue;
+          b_row += p.group_tiles[2 * tile_a] * p.rows_b;
         }
         for (int kb = kb_first; kb < kb_end; ++kb, ++it) {
           const int s = it % PSTAGES;
@@ -563,8 +574,9 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
       int local = 0, s = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const int used = used_tiles();
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        if (p.group_tiles != nullptr && p.group_tiles[2 * ((item / planes) % tiles_a)] < 0) continue;
+        if (a_of(item / planes) >= used) continue;
         const int acc = local & 1, use = local >> 1;
         ++local;
         if (local > 2) ok = mbar_wait(tmem_empty_bar(acc), (use - 1) & 1, abort_flag, p.error, 4);
@@ -598,13 +610,14 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
     const int row_in_tile = quadrant * 32 + lane;
     int local = 0;
     bool ok = true;
+    const int used = used_tiles();
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const int tile = item / planes;
       const size_t plane_offset = (size_t)(item % planes) * p.rows_a * p.ld_out;
-      const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
+      const int tile_a = a_of(tile), tile_b = b_of(tile);
       int rows_end = p.rows_a;                    // rows from here on are not stored
       if (p.group_tiles != nullptr) {
-        if (p.group_tiles[2 * tile_a] < 0) continue;
+        if (tile_a >= used) continue;
         rows_end = min(rows_end, tile_a * BM + p.group_tiles[2 * tile_a + 1]);
       }
       const int acc = local & 1, use = local >> 1;
@@ -866,9 +879,9 @@ PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const
 
 // out[row, n] = x[row, k] . w[g(row)][n, k]^T for the rows of the tiles that `tiles` names: x
 // [max_tiles * 128, k] holds rows sorted by matrix and padded to whole tiles of 128 rows, w is
-// `groups` matrices [n, k] one after another, tiles int32 [max_tiles, 2] gives each tile's matrix
-// (negative: nothing is computed) and how many of its rows are stored. Rows that are not stored
-// keep what out held. out bfloat16 or float32; `activation` as in pae_linear_tcgen05.
+// `groups` matrices [n, k] one after another, tiles int32 [max_tiles + 1, 2] gives each tile's matrix
+// and how many of its rows are stored, and in its last entry how many tiles are in use (the first
+// ones; nothing is computed for the others). Rows that are not stored keep what out held. out bfloat16 or float32; `activation` as in pae_linear_tcgen05.
 PAE_EXPORT int pae_linear_grouped_tcgen05(void* out, const void* x, const void* w, const int* tiles, int max_tiles, int groups,
                                           int n, int k, int out_f32, int activation, int* error, void* stream) {
   if (max_tiles == 0 || n == 0 || groups == 0) return 0;

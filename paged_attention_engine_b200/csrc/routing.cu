@@ -154,7 +154,8 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
 //   rank[i]        the pair's place among its expert's rows (any order: a row's product does not
 //                  depend on where in a tile it lies), -1 for an expert without tensors
 //   first[e]       the expert's first row; tiles[2 j], tiles[2 j + 1]: tile j's expert (-1: unused)
-//                  and how many of its rows are pairs
+//                  and how many of its rows are pairs; the entry after the last tile: how many
+//                  tiles are in use (they are the first ones)
 //   rows[i]        the pair's row, -1 for an expert without tensors
 // ---------------------------------------------------------------------------------------
 __global__ void expert_rank_kernel(int* __restrict__ rank, int* __restrict__ counts, const int* __restrict__ chosen, int pairs,
@@ -175,6 +176,8 @@ __global__ void __launch_bounds__(256) expert_tiles_kernel(int* __restrict__ fir
       first[e] = at * tile;
       at += (counts[e] + tile - 1) / tile;
     }
+    tiles[2 * max_tiles] = min(at, max_tiles);          // the tiles in use are the first ones
+    tiles[2 * max_tiles + 1] = 0;
   }
   __syncthreads();
   for (int j = threadIdx.x; j < max_tiles; j += blockDim.x) {
@@ -250,6 +253,8 @@ __global__ void __launch_bounds__(SMALL_THREADS) expert_plan_small_kernel(int* _
       first[e] = at * tile;
       at += (counts[e] + tile - 1) / tile;
     }
+    tiles[2 * max_tiles] = min(at, max_tiles);
+    tiles[2 * max_tiles + 1] = 0;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
@@ -336,7 +341,7 @@ PAE_EXPORT int pae_expert_max_tiles(int pairs, int experts, int tile) {
 }
 
 // Sorts the pairs chosen [tokens, top] by expert (see above). scratch: int32 [experts] counts, then
-// [experts] first rows, then [tokens * top] ranks. tiles: int32 [max_tiles, 2]; rows: int32
+// [experts] first rows, then [tokens * top] ranks. tiles: int32 [max_tiles + 1, 2]; rows: int32
 // [tokens, top]; staged [max_tiles * tile, width] receives the tokens' inputs x [tokens, width].
 PAE_EXPORT int pae_expert_plan(int* scratch, int* tiles, int* rows, void* staged, const void* x, const int* chosen, int tokens,
                                int top, int experts, int tile, int max_tiles, int width, int dtype, void* stream) {

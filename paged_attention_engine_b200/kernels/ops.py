@@ -1424,12 +1424,14 @@ EXPERT_FEW_PAIRS = 2048
 
 class ExpertPlan:
     """The (token, expert) pairs of a step sorted by expert: `staged` [max_tiles * tile, width] holds
-    the tokens' inputs in rows grouped by expert and padded to whole tiles, `tiles` int32 [max_tiles,
-    2] each tile's expert (negative: unused) and how many of its rows are pairs, `rows` int32
-    [tokens, top] each pair's row (negative: an expert without tensors)."""
+    the tokens' inputs in rows grouped by expert and padded to whole tiles, `tiles` int32 [max_tiles +
+    1, 2] each tile's expert (negative: unused) and how many of its rows are pairs, and in its last
+    entry how many tiles are in use, `rows` int32 [tokens, top] each pair's row (negative: an expert
+    without tensors)."""
 
     def __init__(self, staged, tiles, rows, experts: int) -> None:
         self.staged, self.tiles, self.rows, self.experts = staged, tiles, rows, experts
+        self.max_tiles = tiles.shape[0] - 1
 
 
 def expert_plan(x, chosen, experts: int) -> ExpertPlan:
@@ -1444,7 +1446,7 @@ def expert_plan(x, chosen, experts: int) -> ExpertPlan:
     lib = _lib("routing")
     max_tiles = lib.pae_expert_max_tiles(tokens * top, experts, EXPERT_TILE)
     staged = torch.empty((max_tiles * EXPERT_TILE, x.shape[1]), dtype=x.dtype, device=x.device)
-    tiles = torch.empty((max_tiles, 2), dtype=torch.int32, device=x.device)
+    tiles = torch.empty((max_tiles + 1, 2), dtype=torch.int32, device=x.device)
     rows = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
     scratch = torch.empty((2 * experts + tokens * top,), dtype=torch.int32, device=x.device)
     _check(lib, lib.pae_expert_plan(_ptr(scratch), _ptr(tiles), _ptr(rows), _ptr(staged), _ptr(x), _ptr(chosen), tokens, top, experts,
@@ -1461,11 +1463,11 @@ def linear_grouped(x, weight, plan: ExpertPlan, out_dtype=None, activation: str 
     _need(x, "linear_grouped: x")
     _need(weight, "linear_grouped: weight", x.dtype)
     experts, n, k = weight.shape
-    if x.shape[1] != k or experts != plan.experts or x.shape[0] != plan.tiles.shape[0] * EXPERT_TILE:
-        raise KernelError(f"linear_grouped: x {tuple(x.shape)}, weight {tuple(weight.shape)}, {plan.tiles.shape[0]} tiles of {plan.experts} experts")
+    if x.shape[1] != k or experts != plan.experts or x.shape[0] != plan.max_tiles * EXPERT_TILE:
+        raise KernelError(f"linear_grouped: x {tuple(x.shape)}, weight {tuple(weight.shape)}, {plan.max_tiles} tiles of {plan.experts} experts")
     out_dtype = out_dtype or x.dtype
     out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
-    max_tiles = plan.tiles.shape[0]
+    max_tiles = plan.max_tiles
     if _tensor_core_shape(x, weight, None, out_dtype):
         lib = _lib("gemm_tcgen05")
         _check(lib, lib.pae_linear_grouped_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(plan.tiles), max_tiles, experts, n, k,

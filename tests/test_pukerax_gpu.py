@@ -147,7 +147,9 @@ def test_experts_over_the_chosen_pairs_only(dtype, tokens, top, experts, identit
         row = int(rows[t, k])
         assert int(tiles[row // ops.EXPERT_TILE, 0]) == int(chosen[t, k]) and row % ops.EXPERT_TILE < int(tiles[row // ops.EXPERT_TILE, 1])
         assert torch.equal(plan.staged[row].cpu(), x[t])
-    assert int(tiles[tiles[:, 0] >= 0, 1].sum()) == int(with_tensors.sum())
+    assert int(tiles[:-1][tiles[:-1, 0] >= 0, 1].sum()) == int(with_tensors.sum())
+    used = int(tiles[-1, 0])                                             # the tiles in use are the first ones
+    assert bool((tiles[:used, 0] >= 0).all()) and bool((tiles[used:-1, 0] == -1).all())
     hidden = ops.linear_grouped(plan.staged, up.to(DEV), plan, activation="relu2")
     y = ops.linear_grouped(hidden, down.to(DEV), plan, out_dtype=torch.float32)
     got = ops.expert_combine(y, plan, weights.to(DEV), x.to(DEV), base.to(DEV))
