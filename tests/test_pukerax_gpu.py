@@ -119,7 +119,7 @@ def test_router_without_correction():
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens, top, experts, identity, width, ff", [
     (1, 2, 4, 0, 64, 32), (7, 3, 5, 2, 48, 24), (300, 2, 6, 1, 128, 64), (1200, 2, 6, 1, 128, 64), (900, 4, 16, 0, 64, 200), (130, 1, 3, 3, 72, 40),
-    (260, 2, 2, 0, 256, 96), (50, 2, 4, 1, 44, 20)])
+    (260, 2, 2, 0, 256, 96), (50, 2, 4, 1, 44, 20), (40, 2, 3, 0, 64, 20)])
 def test_experts_over_the_chosen_pairs_only(dtype, tokens, top, experts, identity, width, ff):
     """The pairs sorted by expert, both grouped products and the weighted sum against a loop over
     tokens; an expert with hundreds of pairs (several tiles), experts with none, pairs of experts
