@@ -48,11 +48,13 @@ class LayerSpec:
     kind's own declaration (`roles` of the class registered under `block`): the usual
     decoder block has `mixer_norm`, `mixer`, `feed_forward_norm` and `feed_forward`;
     a block with four norms or one shared norm names its roles otherwise and nothing
-    outside that class changes. `layer.mixer` reads `layer.parts["mixer"]`.
+    outside that class changes. `layer.mixer` reads `layer.parts["mixer"]`. `params` are the
+    constants of the arrangement itself (a multiplier on what a sublayer adds to the stream).
     """
 
     block: str
     parts: Mapping[str, PartSpec]
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     def __getattr__(self, role: str) -> PartSpec:
         parts = object.__getattribute__(self, "parts")
@@ -64,10 +66,13 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer. `cache_from` is the index of an EARLIER schedule entry whose
-    keys and values this run reads instead of writing its own."""
+    keys and values this run reads instead of writing its own. `add_embedding`: the embedding's
+    output joins the residual stream once more right before this run (the first layer of a
+    repeated pass)."""
 
     layer: int
     cache_from: int | None = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -17,6 +17,7 @@ from typing import Any, Callable, Mapping
 from .errors import ConfigError
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .bidonex import BidonexConfig
+from .finezen import FinezenConfig
 from .qwen2 import Qwen2Config
 from .pukerax import PukeraxConfig
 from .zugarax import ZugaraxConfig
@@ -369,3 +370,84 @@ def pukerax_spec(cfg: PukeraxConfig) -> ModelSpec:
 
 
 register_architecture("Pukerax", PukeraxConfig, pukerax_spec)
+
+
+# --------------------------------------------------------------------------- #
+# Finezen: a scaled token embedding into a float32 residual stream; every sublayer between two
+# norms without statistics, x <- x + m * dyt_b(f(dyt_a(x))) with dyt(v) = tanh(alpha v) w + b; the
+# mixer a windowed grouped-query attention (q and k normed over the whole projection, a leading
+# span of each head rotated with ramped frequencies, a learned sink per head, a gate per head) or a
+# windowed latent attention without positions (a query latent, a gate per head); the feed-forward a
+# mixture of gated experts (sigmoid scores taken as weights as they are, on the experts' inputs) with
+# a shared expert behind a sigmoid of its own; a span of layers may run several times with the same
+# weights, a cache per pass, the embedding's output joining the stream again before each further
+# pass; the same norm and an untied head at the end.
+# --------------------------------------------------------------------------- #
+
+# The design has no longest sequence; positions are 32-bit integers.
+FINEZEN_MAX_POSITIONS = 1 << 30
+
+
+def finezen_spec(cfg: FinezenConfig) -> ModelSpec:
+    layers = []
+    for i, layer in enumerate(cfg.layers):
+        prefix = f"l{i}"
+        m = layer.mixer
+        if layer.type == "attention":
+            encoding = None
+            if m.rot is not None:
+                scaling = dict(m.rot.scaling, kind="ramped") if m.rot.scaling is not None else None
+                encoding = {"kind": "scaled_rotary", "dims": m.rot.dims, "base": m.rot.base, "scaling": scaling}
+            mixer = PartSpec(
+                "gated_window_attention",
+                {
+                    "hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
+                    "value_dim": m.vdim, "scale": m.scale, "window": m.window, "qk_norm_eps": cfg.norm_eps, "qk_norm": "whole",
+                    "learned_sink": True, "output_gate": "head", "position_encoding": encoding,
+                },
+                f"{prefix}.mix",
+            )
+        else:
+            mixer = PartSpec(
+                "latent_attention",
+                {
+                    "hidden_size": cfg.width, "num_heads": m.heads, "head_dim": m.dim, "rot_dim": 0, "value_dim": m.vdim,
+                    "kv_rank": m.kv_rank, "q_rank": m.q_rank, "scale": m.scale, "norm_eps": cfg.norm_eps, "window": m.window,
+                    "head_gate": True, "position_encoding": None,
+                },
+                f"{prefix}.mix",
+            )
+        norm = lambda name: PartSpec("dynamic_tanh", {"size": cfg.width},
+                                     names={"weight": f"{prefix}.{name}", "alpha": f"{prefix}.{name}.alpha", "bias": f"{prefix}.{name}.b"})
+        parts = dict(mixer_norm=norm("norm1"), mixer=mixer, mixer_out_norm=norm("norm1b"))
+        if layer.mlp is not None:
+            parts.update(
+                feed_forward_norm=norm("norm2"),
+                feed_forward=PartSpec(
+                    "routed_experts",
+                    {
+                        "hidden_size": cfg.width, "intermediate_size": layer.mlp.ff, "gated": True, "num_experts": layer.mlp.experts,
+                        "top": layer.mlp.top, "score": "sigmoid", "normalize_weights": False, "weight_scale": 1.0,
+                        "weight_on": "input", "shared_size": layer.mlp.shared_ff, "shared_gate": bool(layer.mlp.shared_ff),
+                    },
+                    f"{prefix}.mlp",
+                ),
+                feed_forward_out_norm=norm("norm2b"))
+        layers.append(LayerSpec("sandwich_residual" if layer.mlp is not None else "sandwich_residual_mixer", parts,
+                                {"residual_mult": cfg.residual_mult}))
+    return ModelSpec(
+        architecture=cfg.architecture,
+        vocab_size=cfg.vocab,
+        hidden_size=cfg.width,
+        max_positions=FINEZEN_MAX_POSITIONS,
+        embedding=PartSpec("scaled_token_embedding", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "scale": cfg.embedding_scale},
+                           names={"weight": "embed"}),
+        layers=tuple(layers),
+        schedule=tuple(ScheduleEntry(i, None, add) for i, add in cfg.runs()),
+        final_norm=PartSpec("dynamic_tanh", {"size": cfg.width},
+                            names={"weight": "final.norm", "alpha": "final.norm.alpha", "bias": "final.norm.b"}),
+        head=PartSpec("lm_head", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "tied_to": None}, names={"weight": "head"}),
+    )
+
+
+register_architecture("Finezen", FinezenConfig, finezen_spec)

@@ -1,9 +1,12 @@
 // What stands between a fused projection and attention, for mixers that norm and rotate their
 // heads: per query and key head an optional RMS norm over the head's first channels with a
-// weight shared by all heads, a rotation of a span of the head by the step's table of cosines
-// and sines, in either pairing, and the write of keys (and values) into their pages.
+// weight shared by all heads (or one RMS norm over all query heads of the token at once, and one
+// over all key heads, with a weight as long as the projection), a rotation of a span of the head
+// by the step's table of cosines and sines, in either pairing, and the write of keys (and values)
+// into their pages.
 //
 //   norm      y[i] = x[i] / sqrt(mean(x[0..span)^2) + eps) * w[i]      for i < span; the rest passes
+//   or        y[h, i] = x[h, i] / sqrt(mean over all heads and channels of x^2 + eps) * w[h, i]   ("whole")
 //   rotation  of channels [rot0, rot0 + dims): pair (i, i + dims/2) ("half") or (2i, 2i + 1)
 //             ("interleaved"), i < dims/2:  (u, v) -> (u c_i - v s_i, v c_i + u s_i)
 //   write     q -> q_out[token, head, :]; k -> keys[page, kv head, offset, :]; v likewise
@@ -35,6 +38,8 @@ struct HeadPrep {
   int heads, kv_heads, qd, kd, dv;
   int q_span, k_span, q_rot0, k_rot0, dims, interleaved, page_size;
   float eps;
+  int whole;             // the norm's mean runs over all query (key) heads of the token; weights [heads, span]
+  int whole_kv_heads;    // the key heads that the mean runs over (kv_heads is 0 in a step that writes no page)
 };
 
 constexpr int WARPS = 4;
@@ -56,6 +61,32 @@ __global__ void __launch_bounds__(WARPS * 32) head_prep_kernel(const HeadPrep p)
   }
   const int page = slot >= 0 ? slot / p.page_size : 0, offset = slot >= 0 ? slot - page * p.page_size : 0;
   const int half = p.dims >> 1;
+  // "whole": the token's two sums of squares, by the whole block in an order that depends on
+  // nothing but the sizes (so a token's result is the same in any batch)
+  __shared__ double whole_sum[2][WARPS];
+  float whole_inv[2] = {0.f, 0.f};
+  if (p.whole) {
+    for (int which = 0; which < 2; ++which) {
+      const TI* src = in + (which == 0 ? p.q_off : p.k_off);
+      // keys are normed whether or not the token has a page: the count is the model's, not the step's
+      const int n = which == 0 ? (p.q_norm != nullptr ? p.heads * p.qd : 0) : (p.k_norm != nullptr ? p.whole_kv_heads * p.kd : 0);
+      double squares = 0.0;
+      for (int i = threadIdx.x; i < n; i += WARPS * 32) {
+        const float v = to_float(src[i]);
+        squares = fma((double)v, (double)v, squares);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
+      if (lane == 0) whole_sum[which][warp] = squares;
+    }
+    __syncthreads();
+    for (int which = 0; which < 2; ++which) {
+      const int n = which == 0 ? p.heads * p.qd : p.whole_kv_heads * p.kd;
+      double squares = 0.0;
+      for (int w = 0; w < WARPS; ++w) squares += whole_sum[which][w];
+      whole_inv[which] = n > 0 ? (float)(1.0 / sqrt(squares / (double)n + (double)p.eps)) : 0.f;
+    }
+  }
   for (int unit = blockIdx.y * WARPS + warp; unit < units; unit += WARPS * gridDim.y) {
     const bool is_q = unit < p.heads, is_k = !is_q && unit < p.heads + p.kv_heads;
     const int index = is_q ? unit : (is_k ? unit - p.heads : unit - p.heads - p.kv_heads);
@@ -64,13 +95,18 @@ __global__ void __launch_bounds__(WARPS * 32) head_prep_kernel(const HeadPrep p)
     const TI* src = in + (is_q ? p.q_off : (is_k ? p.k_off : p.v_off)) + (size_t)index * d;
     const float* weight = is_q ? p.q_norm : (is_k ? p.k_norm : nullptr);
     const int span = is_q ? p.q_span : (is_k ? p.k_span : 0);
+    if (p.whole && weight != nullptr) weight += (size_t)index * span;
     double squares = 0.0;
     for (int i = lane; i < d; i += 32) {
       const float v = to_float(src[i]);
       buf[i] = v;
       if (weight != nullptr && i < span) squares = fma((double)v, (double)v, squares);
     }
-    if (weight != nullptr && span > 0) {
+    if (p.whole && weight != nullptr) {
+      const float inv = whole_inv[is_q ? 0 : 1];
+      __syncwarp();
+      for (int i = lane; i < span; i += 32) buf[i] = buf[i] * inv * weight[i];
+    } else if (weight != nullptr && span > 0) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
       const float inv = (float)(1.0 / sqrt(squares / (double)span + (double)p.eps));
@@ -131,12 +167,12 @@ __global__ void sigmoid_gate_kernel(TX* __restrict__ out, const TX* __restrict__
 
 }  // namespace
 
-// in_dtype: the projection's element type; out_dtype: that of q_out and of the pages (0 float32, 1 bfloat16).
+// whole: the norms' means run over all heads at once (weights [heads * span]). in_dtype: the projection's element type; out_dtype: that of q_out and of the pages (0 float32, 1 bfloat16).
 PAE_EXPORT int pae_head_prep(void* q_out, void* keys, void* values, const void* proj, int ld, int q_off, int k_off,
                              int v_off, int tokens, int heads, int kv_heads, int qd, int kd, int dv,
                              const float* q_norm, int q_span, const float* k_norm, int k_span, float eps,
                              const float* table, int dims, int interleaved, int q_rot0, int k_rot0, const int* slots,
-                             int page_size, int in_dtype, int out_dtype, void* stream) {
+                             int page_size, int whole, int in_dtype, int out_dtype, void* stream) {
   if (tokens == 0 || heads + kv_heads == 0) return 0;
   if (heads < 0 || kv_heads < 0 || qd < 0 || kd < 0 || dv < 0) return fail(2, "head_prep: a negative size");
   if (dims % 2) return fail(2, "head_prep: %d rotated channels are not pairs", dims);
@@ -145,9 +181,11 @@ PAE_EXPORT int pae_head_prep(void* q_out, void* keys, void* values, const void* 
   if (q_span > qd || k_span > kd) return fail(2, "head_prep: a norm over %d or %d channels of heads of %d and %d", q_span, k_span, qd, kd);
   if (kv_heads > 0 && slots != nullptr && (keys == nullptr || page_size < 1)) return fail(2, "head_prep: slots without pages");
   if (heads > 0 && q_out == nullptr) return fail(2, "head_prep: query heads without an output");
+  if (whole && ((q_norm != nullptr && q_span != qd) || (k_norm != nullptr && k_span != kd)))
+    return fail(2, "head_prep: a norm over the whole projection covers every channel (%d of %d, %d of %d)", q_span, qd, k_span, kd);
   HeadPrep p{proj, q_out, keys, values, q_norm, k_norm, table, slots, ld, q_off, k_off, v_off, heads,
              slots != nullptr ? kv_heads : 0, qd, kd, dv, q_span, k_span, q_rot0, k_rot0, table != nullptr ? dims : 0,
-             interleaved, page_size < 1 ? 1 : page_size, eps};
+             interleaved, page_size < 1 ? 1 : page_size, eps, whole, kv_heads};
   const int widest = qd > kd ? (qd > dv ? qd : dv) : (kd > dv ? kd : dv);
   const size_t smem = sizeof(float) * WARPS * (size_t)widest;
   if (smem > 48 * 1024) return fail(2, "head_prep: heads of %d channels are too wide", widest);

@@ -5,7 +5,8 @@
 //            experts, a group's score is its largest c and only the `keep` best groups can be
 //            chosen (the others count as minus infinity); the `top` largest c are chosen,
 //            the lower index first among equals
-//   weights  w_e = s_e / (sum of the chosen s + eps) * scale for the chosen, 0 for the others
+//   weights  w_e = s_e / (sum of the chosen s + eps) * scale for the chosen, 0 for the others;
+//            or, not normalized, w_e = s_e * scale
 //
 // One warp per token; all arithmetic float32. The kernel leaves the chosen experts, their weights
 // and, when asked, the dense row of weights [total experts].
@@ -21,14 +22,14 @@ constexpr int WARPS = 4;
 constexpr int MAX_PER_LANE = 16;      // 512 experts
 
 struct Route {
-  const float* logits;       // [splits, tokens, total]: the planes of a split product are added in their order
+  const float* logits;       // [splits, tokens, ld], of which the first `total` columns: the planes of a split product are added in their order
   const float* correction;   // [total] or null
   int* chosen;               // [tokens, top]
   float* weights;            // [tokens, top]
   float* dense;              // [tokens, total] or null
   int tokens, total, top, groups, keep, sigmoid;
   float eps, scale;
-  int splits;
+  int splits, ld, normalize;
 };
 
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
@@ -50,7 +51,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
   if (t >= p.tokens) return;
   float* choice = shared + (size_t)warp * (p.total + p.groups);
   float* group_score = choice + p.total;
-  const float* z = p.logits + (size_t)t * p.total;
+  const float* z = p.logits + (size_t)t * p.ld;
   float s[PER_LANE];
   float top = -FLT_MAX;
 #pragma unroll
@@ -59,7 +60,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
     s[j] = -FLT_MAX;
     if (e < p.total) {
       float sum = z[e];
-      for (int k = 1; k < p.splits; ++k) sum += z[(size_t)k * p.tokens * p.total + e];
+      for (int k = 1; k < p.splits; ++k) sum += z[(size_t)k * p.tokens * p.ld + e];
       s[j] = sum;
     }
     top = fmaxf(top, s[j]);
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_kernel(const Route p) {
     }
   }
   __syncwarp();
-  const float factor = p.scale / (chosen_sum + p.eps);
+  const float factor = p.normalize ? p.scale / (chosen_sum + p.eps) : p.scale;
   for (int k = lane; k < p.top; k += 32) {
     const float w = p.weights[(size_t)t * p.top + k] * factor;
     p.weights[(size_t)t * p.top + k] = w;
@@ -198,7 +199,8 @@ __global__ void __launch_bounds__(256) expert_tiles_kernel(int* __restrict__ fir
 template <typename T>
 __global__ void __launch_bounds__(128) expert_gather_kernel(T* __restrict__ staged, int* __restrict__ rows, const T* __restrict__ x,
                                                             const int* __restrict__ chosen, const int* __restrict__ rank,
-                                                            const int* __restrict__ first, int top, int width, int max_rows) {
+                                                            const int* __restrict__ first, const float* __restrict__ scale, int top,
+                                                            int width, int max_rows) {
   dependent_launch_prologue();
   const int i = blockIdx.x;
   const int r = rank[i];
@@ -211,7 +213,10 @@ __global__ void __launch_bounds__(128) expert_gather_kernel(T* __restrict__ stag
   if (row < 0) return;
   const T* src = x + (size_t)(i / top) * width;
   T* dst = staged + (size_t)row * width;
-  if (((sizeof(T) * width) & 15) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+  if (scale != nullptr) {                               // an expert that is weighted on its input
+    const float w = scale[i];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = from_float<T>(w * to_float(src[c]));
+  } else if (((sizeof(T) * width) & 15) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
     const int n = (int)(sizeof(T) * width / 16);
     for (int c = threadIdx.x; c < n; c += blockDim.x) ((int4*)dst)[c] = ((const int4*)src)[c];
   } else {
@@ -226,8 +231,8 @@ constexpr int SMALL_PAIRS = 2048, SMALL_THREADS = 1024;
 template <typename T>
 __global__ void __launch_bounds__(SMALL_THREADS) expert_plan_small_kernel(int* __restrict__ tiles, int* __restrict__ rows,
                                                                           T* __restrict__ staged, const T* __restrict__ x,
-                                                                          const int* __restrict__ chosen, int pairs, int top,
-                                                                          int experts, int tile, int max_tiles, int width) {
+                                                                          const int* __restrict__ chosen, const float* __restrict__ scale,
+                                                                          int pairs, int top, int experts, int tile, int max_tiles, int width) {
   dependent_launch_prologue();
   __shared__ int counts[32 * MAX_PER_LANE], first[32 * MAX_PER_LANE], row_of[SMALL_PAIRS];
   for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
@@ -281,7 +286,10 @@ __global__ void __launch_bounds__(SMALL_THREADS) expert_plan_small_kernel(int* _
     if (row < 0) continue;
     const T* src = x + (size_t)(i / top) * width;
     T* dst = staged + (size_t)row * width;
-    if (((sizeof(T) * width) & 15) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+    if (scale != nullptr) {
+      const float w = scale[i];
+      for (int c = lane; c < width; c += 32) dst[c] = from_float<T>(w * to_float(src[c]));
+    } else if (((sizeof(T) * width) & 15) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
       const int n16 = (int)(sizeof(T) * width / 16);
       for (int c = lane; c < n16; c += 32) ((int4*)dst)[c] = ((const int4*)src)[c];
     } else {
@@ -292,10 +300,13 @@ __global__ void __launch_bounds__(SMALL_THREADS) expert_plan_small_kernel(int* _
 
 // out[t, :] = (base[t, :], itself the sum of base_planes planes) + sum over the token's chosen experts k, in the order of the choice, of
 // weights[t, k] * (y[rows[t, k], :] for an expert with tensors, x[t, :] for one that returns its input).
+// weights null: every weight is 1. gate (or null): base[t, :] is first multiplied by sigmoid(gate[t, gate_col]),
+// the gate itself the sum of gate_planes planes of rows of gate_ld.
 template <typename T>
 __global__ void expert_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ rows,
                                       const float* __restrict__ weights, const T* __restrict__ x, const float* __restrict__ base,
-                                      int base_planes, int top, int width, long long total) {
+                                      int base_planes, const float* __restrict__ gate, int gate_planes, int gate_ld, int gate_col,
+                                      long long tokens, int top, int width, long long total) {
   dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -304,9 +315,14 @@ __global__ void expert_combine_kernel(float* __restrict__ out, const float* __re
   float acc = 0.f;                                    // base: the planes of a split product, added in their order
   if (base != nullptr)
     for (int k = 0; k < base_planes; ++k) acc += base[(size_t)k * total + i];
+  if (gate != nullptr) {
+    float g = 0.f;
+    for (int k = 0; k < gate_planes; ++k) g += gate[((size_t)k * tokens + t) * gate_ld + gate_col];
+    acc = acc / (1.f + expf(-g));
+  }
   for (int k = 0; k < top; ++k) {
     const int row = rows[t * top + k];
-    const float w = weights[t * top + k];
+    const float w = weights != nullptr ? weights[t * top + k] : 1.f;
     acc += w * (row >= 0 ? y[(size_t)row * width + c] : to_float(x[i]));
   }
   out[i] = acc;
@@ -314,15 +330,16 @@ __global__ void expert_combine_kernel(float* __restrict__ out, const float* __re
 
 }  // namespace
 
-PAE_EXPORT int pae_route(int* chosen, float* weights, float* dense, const float* logits, int splits, const float* correction, int tokens,
-                         int total, int top, int groups, int keep, int sigmoid, float eps, float scale, void* stream) {
+PAE_EXPORT int pae_route(int* chosen, float* weights, float* dense, const float* logits, int splits, int ld, const float* correction, int tokens,
+                         int total, int top, int groups, int keep, int sigmoid, int normalize, float eps, float scale, void* stream) {
   if (tokens == 0) return 0;
   if (total < 1 || total > 32 * MAX_PER_LANE) return fail(2, "route: %d experts (1 to %d)", total, 32 * MAX_PER_LANE);
   if (top < 1 || top > total) return fail(2, "route: %d of %d experts", top, total);
   if (groups < 0 || (groups > 0 && (total % groups || keep < 1 || keep > groups || top > total / groups * keep)))
     return fail(2, "route: %d experts in %d groups of which %d are kept, %d chosen", total, groups, keep, top);
   if (splits < 1) return fail(2, "route: %d planes of logits", splits);
-  Route p{logits, correction, chosen, weights, dense, tokens, total, top, groups, keep, sigmoid, eps, scale, splits};
+  if (ld < total) return fail(2, "route: %d experts in rows of %d", total, ld);
+  Route p{logits, correction, chosen, weights, dense, tokens, total, top, groups, keep, sigmoid, eps, scale, splits, ld, normalize};
   const size_t smem = sizeof(float) * WARPS * (size_t)(total + groups);
   const unsigned blocks = (tokens + WARPS - 1) / WARPS;
   cudaStream_t s = (cudaStream_t)stream;
@@ -340,11 +357,12 @@ PAE_EXPORT int pae_expert_max_tiles(int pairs, int experts, int tile) {
   return (pairs < experts ? pairs : experts) + pairs / tile;
 }
 
-// Sorts the pairs chosen [tokens, top] by expert (see above). scratch: int32 [experts] counts, then
+// Sorts the pairs chosen [tokens, top] by expert (see above). scale: float32 [tokens, top] or null; with it a
+// pair's staged row is scale * the token's input, rounded once. scratch: int32 [experts] counts, then
 // [experts] first rows, then [tokens * top] ranks. tiles: int32 [max_tiles + 1, 2]; rows: int32
 // [tokens, top]; staged [max_tiles * tile, width] receives the tokens' inputs x [tokens, width].
-PAE_EXPORT int pae_expert_plan(int* scratch, int* tiles, int* rows, void* staged, const void* x, const int* chosen, int tokens,
-                               int top, int experts, int tile, int max_tiles, int width, int dtype, void* stream) {
+PAE_EXPORT int pae_expert_plan(int* scratch, int* tiles, int* rows, void* staged, const void* x, const int* chosen, const float* scale,
+                               int tokens, int top, int experts, int tile, int max_tiles, int width, int dtype, void* stream) {
   const int pairs = tokens * top;
   if (pairs == 0) return 0;
   if (experts < 1 || tile < 1 || max_tiles < pae_expert_max_tiles(pairs, experts, tile))
@@ -353,9 +371,9 @@ PAE_EXPORT int pae_expert_plan(int* scratch, int* tiles, int* rows, void* staged
   if (dtype != kF32 && dtype != kBF16) return fail(1, "expert_plan: unknown dtype %d", dtype);
   if (pairs <= SMALL_PAIRS && experts <= 32 * MAX_PER_LANE) {
     if (dtype == kF32)
-      launch_kernel(expert_plan_small_kernel<float>, 1, SMALL_THREADS, 0, s, tiles, rows, (float*)staged, (const float*)x, chosen, pairs, top, experts, tile, max_tiles, width);
+      launch_kernel(expert_plan_small_kernel<float>, 1, SMALL_THREADS, 0, s, tiles, rows, (float*)staged, (const float*)x, chosen, scale, pairs, top, experts, tile, max_tiles, width);
     else
-      launch_kernel(expert_plan_small_kernel<__nv_bfloat16>, 1, SMALL_THREADS, 0, s, tiles, rows, (__nv_bfloat16*)staged, (const __nv_bfloat16*)x, chosen, pairs, top, experts, tile, max_tiles, width);
+      launch_kernel(expert_plan_small_kernel<__nv_bfloat16>, 1, SMALL_THREADS, 0, s, tiles, rows, (__nv_bfloat16*)staged, (const __nv_bfloat16*)x, chosen, scale, pairs, top, experts, tile, max_tiles, width);
     return check_launch("expert_plan");
   }
   int *counts = scratch, *first = scratch + experts, *rank = scratch + 2 * experts;
@@ -365,21 +383,22 @@ PAE_EXPORT int pae_expert_plan(int* scratch, int* tiles, int* rows, void* staged
   launch_kernel(expert_tiles_kernel, 1, 256, 0, s, first, tiles, (const int*)counts, experts, tile, max_tiles);
   const int max_rows = max_tiles * tile;
   if (dtype == kF32)
-    launch_kernel(expert_gather_kernel<float>, pairs, 128, 0, s, (float*)staged, rows, (const float*)x, chosen, (const int*)rank, (const int*)first, top, width, max_rows);
+    launch_kernel(expert_gather_kernel<float>, pairs, 128, 0, s, (float*)staged, rows, (const float*)x, chosen, (const int*)rank, (const int*)first, scale, top, width, max_rows);
   else if (dtype == kBF16)
-    launch_kernel(expert_gather_kernel<__nv_bfloat16>, pairs, 128, 0, s, (__nv_bfloat16*)staged, rows, (const __nv_bfloat16*)x, chosen, (const int*)rank, (const int*)first, top, width, max_rows);
+    launch_kernel(expert_gather_kernel<__nv_bfloat16>, pairs, 128, 0, s, (__nv_bfloat16*)staged, rows, (const __nv_bfloat16*)x, chosen, (const int*)rank, (const int*)first, scale, top, width, max_rows);
   else return fail(1, "expert_plan: unknown dtype %d", dtype);
   return check_launch("expert_plan");
 }
 
 PAE_EXPORT int pae_expert_combine(float* out, const float* y, const int* rows, const float* weights, const void* x, const float* base,
-                                  int base_planes, int tokens, int top, int width, int dtype, void* stream) {
+                                  int base_planes, const float* gate, int gate_planes, int gate_ld, int gate_col, int tokens, int top,
+                                  int width, int dtype, void* stream) {
   const long long total = (long long)tokens * width;
   if (total == 0) return 0;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == kF32) launch_kernel(expert_combine_kernel<float>, blocks, 256, 0, s, out, y, rows, weights, (const float*)x, base, base_planes, top, width, total);
-  else if (dtype == kBF16) launch_kernel(expert_combine_kernel<__nv_bfloat16>, blocks, 256, 0, s, out, y, rows, weights, (const __nv_bfloat16*)x, base, base_planes, top, width, total);
+  if (dtype == kF32) launch_kernel(expert_combine_kernel<float>, blocks, 256, 0, s, out, y, rows, weights, (const float*)x, base, base_planes, gate, gate_planes, gate_ld, gate_col, (long long)tokens, top, width, total);
+  else if (dtype == kBF16) launch_kernel(expert_combine_kernel<__nv_bfloat16>, blocks, 256, 0, s, out, y, rows, weights, (const __nv_bfloat16*)x, base, base_planes, gate, gate_planes, gate_ld, gate_col, (long long)tokens, top, width, total);
   else return fail(1, "expert_combine: unknown dtype %d", dtype);
   return check_launch("expert_combine");
 }

@@ -50,7 +50,9 @@ class DecoderModel:
                 role: REGISTRIES[registry].get(part.kind)(part, tensors, runtime)
                 for role, registry, part in layer_part_specs(layer)
             }
-            self.layers.append(Layer(BLOCKS.get(layer.block)(), built))
+            block = BLOCKS.get(layer.block)()
+            block.params = dict(layer.params)
+            self.layers.append(Layer(block, built))
         self.forward_pass_count = 0
         self.graph_safe = all(getattr(part, "graph_safe", True) for part in self.parts())
 
@@ -67,11 +69,13 @@ class DecoderModel:
         self.forward_pass_count += 1
         if NVTX:
             torch.cuda.nvtx.range_push(f"traversal: {ctx.num_tokens} tokens of {ctx.num_seqs} requests")
-        hidden = self.embedding.forward(ctx)
+        hidden = embedded = self.embedding.forward(ctx)
         for position, entry in enumerate(self.spec.schedule):
             layer = self.layers[entry.layer]
             if NVTX:
                 torch.cuda.nvtx.range_push(f"entry {position}: layer {entry.layer}")
+            if entry.add_embedding:
+                hidden = self.ops.join_stream(hidden, embedded)        # pending: the next norm's kernel adds it
             hidden = layer.block.forward(ctx, hidden, layer, entry_caches[position])
             if NVTX:
                 torch.cuda.nvtx.range_pop()

@@ -56,6 +56,7 @@ FAMILIES: dict[str, list[str]] = {
     "linear_heads": ["linear_heads.cu", "attention_mma.cuh", "common.cuh"],
     "streams": ["streams.cu", "common.cuh"],
     "routing": ["routing.cu", "common.cuh"],
+    "dyt": ["dyt.cu", "common.cuh"],
     "attention_decode_noalloc": [
         "attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_mma.cuh", "common.cuh",
     ],

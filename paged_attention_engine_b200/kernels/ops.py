@@ -225,8 +225,33 @@ class PendingStreams:
         return self.x.device
 
 
+class PendingResidual:
+    """A float32 residual stream x + mult * post(y) (+ extra) whose sum has not been made: `residual_add`
+    returns one, and the norm without statistics that reads the stream next (`dyt_norm`) makes the
+    sum inside its own kernel; anything else calls `materialized`, which runs the sum alone. `post`
+    is (alpha, weight, bias) of a Dynamic Tanh applied to y first, or None; y may be a product that is
+    still in its splits; `extra` is a second stream that joins (or None)."""
+
+    def __init__(self, x, y, post, mult: float, extra=None) -> None:
+        self.x, self.y, self.post, self.mult, self.extra = x, y, post, float(mult), extra
+        self.dtype = torch.float32
+        self.value = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def device(self):
+        return self.x.device
+
+
 def materialized(x):
-    """The tensor that `x` stands for (x itself unless it is a PendingSum, a PendingNorm or PendingStreams)."""
+    """The tensor that `x` stands for (x itself unless it is a PendingSum, a PendingNorm, PendingStreams or a PendingResidual)."""
+    if isinstance(x, PendingResidual):
+        if x.value is None:
+            _dyt_step(x, None, None)
+        return x.value
     if isinstance(x, PendingNorm):
         if x.value is None:
             x.value = _rms_norm_now(x.x, x.weight, x.eps)
@@ -978,10 +1003,12 @@ def softcap(logits, cap: float) -> torch.Tensor:
 
 def head_prep(proj, *, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, q_dim: int, k_dim: int, value_dim: int,
               q_norm, k_norm, q_span: int, k_span: int, eps: float, table, interleaved: bool, q_rot0: int, k_rot0: int,
-              slots, keys, values, page_size: int, out_dtype) -> torch.Tensor:
+              slots, keys, values, page_size: int, out_dtype, whole: bool = False) -> torch.Tensor:
     """From a fused projection [tokens, ld] to attention's operands (csrc/head_prep.cu): every
     query head (q_dim channels at q_off) and key head (k_dim channels at k_off) is RMS-normed over
-    its first q_span / k_span channels with the weight q_norm / k_norm (None: not normed), the span
+    its first q_span / k_span channels with the weight q_norm / k_norm (None: not normed; `whole`:
+    ONE norm over all query heads of the token and one over all key heads, the weights as long as
+    those projections), the span
     of `table.shape[1]` channels from q_rot0 / k_rot0 is rotated by the table (pairs (i, i + half),
     or (2i, 2i + 1) when `interleaved`), the queries are returned as [tokens, heads * q_dim] in
     `out_dtype`, and keys and values (value_dim channels at v_off; `values` None: none) are written
@@ -994,11 +1021,11 @@ def head_prep(proj, *, q_off: int, k_off: int, v_off: int, heads: int, kv_heads:
                (v_off + kv_heads * value_dim) if writes and values is not None else 0)
     if need > ld:
         raise KernelError(f"head_prep: columns up to {need} of rows of {ld}")
-    for name, t, n in (("q_norm", q_norm, q_span), ("k_norm", k_norm, k_span)):
-        if t is not None:
+    for name, t, n in (("q_norm", q_norm, q_span * (heads if whole else 1)), ("k_norm", k_norm, k_span * (kv_heads if whole else 1))):
+        if t is not None and n > 0:
             _need(t, f"head_prep: {name}", torch.float32)
             if t.numel() != n:
-                raise KernelError(f"head_prep: {name} has {t.numel()} numbers for a span of {n}")
+                raise KernelError(f"head_prep: {name} has {t.numel()} numbers, {n} are needed")
     dims = 0
     if table is not None:
         _need(table, "head_prep: table", torch.float32)
@@ -1017,7 +1044,7 @@ def head_prep(proj, *, q_off: int, k_off: int, v_off: int, heads: int, kv_heads:
         _ptr(q), _ptr(keys if writes else None), _ptr(values if writes else None), _ptr(proj), ld, q_off, k_off, v_off, tokens,
         heads, kv_heads if writes else 0, q_dim, k_dim, value_dim if values is not None else 0, _ptr(q_norm), q_span,
         _ptr(k_norm), k_span, float(eps), _ptr(table), dims, 1 if interleaved else 0, q_rot0, k_rot0,
-        _ptr(slots if writes else None), page_size, _code(proj), _DTYPE_CODE[out_dtype], _stream()))
+        _ptr(slots if writes else None), page_size, 1 if whole else 0, _code(proj), _DTYPE_CODE[out_dtype], _stream()))
     return q
 
 
@@ -1323,6 +1350,78 @@ def delta_rule(proj, offsets, w_pre, w0, a_bias, gate_offset, norm_weight, state
 
 
 # ----------------------------------------------------------------------------------- #
+# Norms without statistics around both sides of a sublayer (csrc/dyt.cu)
+
+def _dyt_step(pending, next_norm, out_dtype):
+    """Runs the sum of a PendingResidual (or, for a plain tensor, nothing) and, with `next_norm` =
+    (alpha, weight, bias), the Dynamic Tanh of the result in `out_dtype`: one kernel. Keeps the new
+    stream in `pending.value` and returns the normed rows or None."""
+    if isinstance(pending, PendingResidual):
+        x, y, post, mult, extra = materialized(pending.x), pending.y, pending.post, pending.mult, materialized(pending.extra)
+    else:
+        x, y, post, mult, extra = pending, None, None, 0.0, None
+    _need(x, "dyt: the stream", torch.float32)
+    tokens, width = x.shape
+    planes = 1
+    if y is not None:
+        y, planes = _sublayer_output(y)
+        if tuple(y.shape[-2:]) != (tokens, width):
+            raise KernelError(f"dyt: a sublayer's output {tuple(y.shape)} for a stream {tuple(x.shape)}")
+    if extra is not None:
+        _need(extra, "dyt: the joining stream", torch.float32)
+        if tuple(extra.shape) != (tokens, width):
+            raise KernelError(f"dyt: a joining stream {tuple(extra.shape)} for a stream {tuple(x.shape)}")
+    for name, norm in (("the norm after the sublayer", post), ("the next norm", next_norm)):
+        if norm is not None:
+            alpha, weight, bias = norm
+            _need(alpha, f"dyt: alpha of {name}", torch.float32)
+            _need(weight, f"dyt: weight of {name}", torch.float32)
+            if weight.numel() != width or alpha.numel() != 1 or (bias is not None and bias.numel() != width):
+                raise KernelError(f"dyt: {name} has {weight.numel()} weights for rows of {width}")
+            if bias is not None:
+                _need(bias, f"dyt: bias of {name}", torch.float32)
+    writes = y is not None or extra is not None
+    x_new = torch.empty_like(x) if writes else None
+    normed = torch.empty((tokens, width), dtype=out_dtype, device=x.device) if next_norm is not None else None
+    post = post or (None, None, None)
+    nxt = next_norm or (None, None, None)
+    if writes or normed is not None:
+        lib = _lib("dyt")
+        _check(lib, lib.pae_dyt_step(_ptr(x_new), _ptr(normed), _ptr(x), _ptr(y), planes, _ptr(extra), _ptr(post[0]), _ptr(post[1]),
+                                     _ptr(post[2]), float(mult), _ptr(nxt[0]), _ptr(nxt[1]), _ptr(nxt[2]), tokens, width,
+                                     _DTYPE_CODE[out_dtype] if out_dtype is not None else 0, _stream()))
+    if isinstance(pending, PendingResidual):
+        pending.value = x_new if writes else x
+    return normed
+
+
+def dyt_norm(x, alpha, weight, bias, out_dtype) -> torch.Tensor:
+    """tanh(alpha * x) * weight + bias in `out_dtype`: x float32 [tokens, width], or a residual sum
+    that is still pending, which this kernel makes on the way (`materialized(x)` then has it)."""
+    if isinstance(x, PendingResidual) and x.value is None:
+        return _dyt_step(x, (alpha, weight, bias), out_dtype)
+    x = materialized(x)
+    if x.dtype != torch.float32:
+        raise KernelError(f"dyt_norm: the stream is {x.dtype}, float32 is needed")
+    return _dyt_step(x, (alpha, weight, bias), out_dtype)
+
+
+def residual_add(x, y, mult: float = 1.0, post=None):
+    """The stream x + mult * post(y), float32, pending: `post` = (alpha, weight, bias) of a Dynamic Tanh
+    over y, or None. The next `dyt_norm` makes the sum in its own kernel."""
+    return PendingResidual(x, y, post, mult)
+
+
+def join_stream(x, extra):
+    """The stream x + extra (both float32 [tokens, width]), pending; a pending residual sum takes
+    `extra` along in its own kernel."""
+    if isinstance(x, PendingResidual) and x.value is None and x.extra is None:
+        x.extra = extra
+        return x
+    return PendingResidual(materialized(x), None, None, 0.0, extra)
+
+
+# ----------------------------------------------------------------------------------- #
 # Hyper-connections (csrc/streams.cu) and routed experts (csrc/routing.cu)
 
 def _sublayer_output(y):
@@ -1393,15 +1492,21 @@ def streams_read_norm(x, in_w, norm_w: torch.Tensor, eps: float, streams: int, o
 
 
 def route(logits, correction, top: int, groups: int = 0, keep: int = 0, score: str = "softmax", eps: float = 0.0,
-          scale: float = 1.0, dense: bool = True):
+          scale: float = 1.0, dense: bool = True, normalize: bool = True, experts: int | None = None):
     """Chooses `top` experts per token from float32 router logits [tokens, experts] (csrc/routing.cu):
     scores softmax (or sigmoid) of the logits, the choice by score + correction among the experts of
     the `keep` best of `groups` groups (0: all experts), weights score / (sum of the chosen + eps) *
-    scale. -> (chosen int32 [tokens, top], weights float32 [tokens, top], dense float32 [tokens,
-    experts] with the weights at the chosen experts' columns and 0 elsewhere, or None when `dense` is False)."""
+    scale (`normalize` False: score * scale, the chosen scores as they are). `experts` (default: every
+    column): the router's outputs are the first `experts` columns of wider rows, whose other columns
+    (a gate that the same product computes) are not looked at. -> (chosen int32 [tokens, top], weights
+    float32 [tokens, top], dense float32 [tokens, experts] with the weights at the chosen experts'
+    columns and 0 elsewhere, or None when `dense` is False)."""
     logits, splits = _sublayer_output(logits)         # a split product's planes are added by the kernel itself
     _need(logits, "route: logits", torch.float32)
-    tokens, total = logits.shape[-2:]
+    tokens, ld = logits.shape[-2:]
+    total = ld if experts is None else int(experts)
+    if total > ld:
+        raise KernelError(f"route: {total} experts in rows of {ld}")
     if correction is not None:
         _need(correction, "route: correction", torch.float32)
         if correction.numel() != total:
@@ -1412,8 +1517,8 @@ def route(logits, correction, top: int, groups: int = 0, keep: int = 0, score: s
     weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
     dense = torch.empty((tokens, total), dtype=torch.float32, device=logits.device) if dense else None
     lib = _lib("routing")
-    _check(lib, lib.pae_route(_ptr(chosen), _ptr(weights), _ptr(dense), _ptr(logits), splits, _ptr(correction), tokens, total, top,
-                              groups, keep, 1 if score == "sigmoid" else 0, float(eps), float(scale), _stream()))
+    _check(lib, lib.pae_route(_ptr(chosen), _ptr(weights), _ptr(dense), _ptr(logits), splits, ld, _ptr(correction), tokens, total, top,
+                              groups, keep, 1 if score == "sigmoid" else 0, 1 if normalize else 0, float(eps), float(scale), _stream()))
     return chosen, weights, dense
 
 
@@ -1434,23 +1539,28 @@ class ExpertPlan:
         self.max_tiles = tiles.shape[0] - 1
 
 
-def expert_plan(x, chosen, experts: int) -> ExpertPlan:
+def expert_plan(x, chosen, experts: int, input_weights=None) -> ExpertPlan:
     """Sorts the pairs of `chosen` int32 [tokens, top] by expert and copies every pair's input row
     of x [tokens, width] into the staging matrix (csrc/routing.cu). Experts from `experts` on have no
-    tensors and get no rows. Every shape depends on (tokens, top, experts) alone, so a replayed step
-    keeps its buffers."""
+    tensors and get no rows. `input_weights` float32 [tokens, top]: a pair's row is its weight times
+    the token's input (float32 product, rounded once), for experts that are weighted on their input.
+    Every shape depends on (tokens, top, experts) alone, so a replayed step keeps its buffers."""
     x = materialized(x)
     _need(x, "expert_plan: x")
     _need(chosen, "expert_plan: chosen", torch.int32)
     tokens, top = chosen.shape
+    if input_weights is not None:
+        _need(input_weights, "expert_plan: input weights", torch.float32)
+        if tuple(input_weights.shape) != (tokens, top):
+            raise KernelError(f"expert_plan: weights {tuple(input_weights.shape)} for {tokens} x {top} pairs")
     lib = _lib("routing")
     max_tiles = lib.pae_expert_max_tiles(tokens * top, experts, EXPERT_TILE)
     staged = torch.empty((max_tiles * EXPERT_TILE, x.shape[1]), dtype=x.dtype, device=x.device)
     tiles = torch.empty((max_tiles + 1, 2), dtype=torch.int32, device=x.device)
     rows = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
     scratch = torch.empty((2 * experts + tokens * top,), dtype=torch.int32, device=x.device)
-    _check(lib, lib.pae_expert_plan(_ptr(scratch), _ptr(tiles), _ptr(rows), _ptr(staged), _ptr(x), _ptr(chosen), tokens, top, experts,
-                                    EXPERT_TILE, max_tiles, x.shape[1], _code(x), _stream()),
+    _check(lib, lib.pae_expert_plan(_ptr(scratch), _ptr(tiles), _ptr(rows), _ptr(staged), _ptr(x), _ptr(chosen), _ptr(input_weights), tokens, top,
+                                    experts, EXPERT_TILE, max_tiles, x.shape[1], _code(x), _stream()),
            1 if tokens * top <= EXPERT_FEW_PAIRS else 4)
     return ExpertPlan(staged, tiles, rows, experts)
 
@@ -1480,23 +1590,36 @@ def linear_grouped(x, weight, plan: ExpertPlan, out_dtype=None, activation: str 
     return out
 
 
-def expert_combine(y, plan: ExpertPlan, weights, x, base=None) -> torch.Tensor:
+def expert_combine(y, plan: ExpertPlan, weights, x, base=None, base_gate=None) -> torch.Tensor:
     """float32 out[t] = (base[t]) + sum over the token's chosen experts, in the order of the choice, of
     weights[t, k] * (y[rows[t, k]] for an expert with tensors, x[t] for one that returns its input).
-    y float32 [rows, width] (or None when no expert has tensors), x [tokens, width], base float32."""
+    y float32 [rows, width] (or None when no expert has tensors), x [tokens, width], base float32.
+    `weights` None: every weight is 1 (experts that were weighted on their input). `base_gate` =
+    (float32 rows [tokens, ld], column): base[t] is multiplied by the sigmoid of that column first."""
     x = materialized(x)
     planes = 1
     if base is not None:
         base, planes = _sublayer_output(base)
     _need(x, "expert_combine: x")
-    _need(weights, "expert_combine: weights", torch.float32)
+    gate, gate_planes, gate_ld, gate_col = None, 1, 0, 0
+    if base_gate is not None:
+        gate_col = int(base_gate[1])
+        gate, gate_planes = _sublayer_output(base_gate[0])        # a split product's planes are added by the kernel itself
+        gate_ld = int(gate.shape[-1])
+        if base is None or gate.shape[-2] != x.shape[0] or not 0 <= gate_col < gate_ld:
+            raise KernelError(f"expert_combine: a gate {tuple(gate.shape)}, column {gate_col}, for {x.shape[0]} tokens' base")
+    if weights is None:
+        top = int(plan.rows.shape[1])
+    else:
+        _need(weights, "expert_combine: weights", torch.float32)
+        top = int(weights.shape[1])
     if y is not None:
         _need(y, "expert_combine: y", torch.float32)
     if base is not None:
         _need(base, "expert_combine: base", torch.float32)
     out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
     lib = _lib("routing")
-    _check(lib, lib.pae_expert_combine(_ptr(out), _ptr(y), _ptr(plan.rows), _ptr(weights), _ptr(x), _ptr(base), planes, x.shape[0],
-                                       weights.shape[1], x.shape[1], _code(x), _stream()))
+    _check(lib, lib.pae_expert_combine(_ptr(out), _ptr(y), _ptr(plan.rows), _ptr(weights), _ptr(x), _ptr(base), planes, _ptr(gate), gate_planes,
+                                       gate_ld, gate_col, x.shape[0], top, x.shape[1], _code(x), _stream()))
     return out
 

@@ -188,6 +188,8 @@ class Block:
 
     graph_safe = True
     roles: dict[str, str] = {}
+    # the constants of the layer's arrangement itself (`LayerSpec.params`), set when the model is built
+    params: dict = {}
 
     def forward(self, ctx, hidden, layer, cache):
         raise NotImplementedError

@@ -74,3 +74,41 @@ class HyperConnectedMixer(Block):
     def forward(self, ctx, hidden, layer, cache):
         out = layer.mixer.forward(ctx, layer.mixer_norm.forward(ctx, hidden), None, cache)
         return layer.mixer_merge.forward(ctx, ctx.ops.materialized(hidden), out)
+
+
+@BLOCKS.register("sandwich_residual")
+class SandwichResidual(Block):
+    """A norm on both sides of each sublayer: x <- x + m * norm_b(mixer(norm_a(x))), then the same
+    around the feed-forward, with the layer's `residual_mult` m (`params` of the LayerSpec; 1 when
+    absent). The sublayers get no residual and leave float32; the norm after a sublayer adds its
+    result to the stream (`add_to`, or for a norm without one its `forward` and a plain scaled sum),
+    and that sum stays pending until the next norm reads the stream."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_out_norm": "norm",
+             "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_out_norm": "norm"}
+
+    def _add(self, ctx, norm, stream, y):
+        mult = float(self.params.get("residual_mult", 1.0))
+        if hasattr(norm, "add_to"):
+            return norm.add_to(ctx, stream, y, mult)
+        return ctx.ops.residual_add(stream, norm.forward(ctx, ctx.ops.materialized(y)), mult)
+
+    def forward(self, ctx, hidden, layer, cache):
+        normed = layer.mixer_norm.forward(ctx, hidden)
+        out = layer.mixer.forward(ctx, normed, None, cache)
+        hidden = self._add(ctx, layer.mixer_out_norm, ctx.ops.materialized(hidden), out)
+        normed = layer.feed_forward_norm.forward(ctx, hidden)
+        out = layer.feed_forward.forward(ctx, normed, None)
+        return self._add(ctx, layer.feed_forward_out_norm, ctx.ops.materialized(hidden), out)
+
+
+@BLOCKS.register("sandwich_residual_mixer")
+class SandwichResidualMixer(SandwichResidual):
+    """A sandwich-normed layer without a feed-forward."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_out_norm": "norm"}
+
+    def forward(self, ctx, hidden, layer, cache):
+        normed = layer.mixer_norm.forward(ctx, hidden)
+        out = layer.mixer.forward(ctx, normed, None, cache)
+        return self._add(ctx, layer.mixer_out_norm, ctx.ops.materialized(hidden), out)

@@ -1,12 +1,14 @@
-"""Grouped-query attention with normed, partly rotated heads, a unit sink and an output gate.
+"""Grouped-query attention with normed, partly rotated heads, a sink and an output gate.
 
 q, k, v and the gate are one fused projection without bias (float32 out). Every query and key
-head is RMS-normed over its channels with a weight that all heads share, then a leading span of
-the head is rotated (pairs (i, i + span/2)) by the layer's position encoding; keys and values go
-to their pages. Query i sees key j <= i with i - j < window (no window: every earlier key). The
-softmax's denominator may hold an extra 1 (a sink whose logit is 0 and which has no value), and
-the concatenated heads may be multiplied by sigmoid(W_g h) before the output projection, which
-takes the residual in its epilogue. Value heads may have another size than key heads.
+head is RMS-normed over its channels with a weight that all heads share (or all query heads of a
+token are normed at once, and all its key heads, with weights as long as those projections), then
+a leading span of the head is rotated (pairs (i, i + span/2)) by the layer's position encoding;
+keys and values go to their pages. Query i sees key j <= i with i - j < window (no window: every
+earlier key). The softmax's denominator may hold one more term exp(s_h) without a value (a sink:
+s_h = 0, or a learned number per head), and the concatenated heads may be multiplied by
+sigmoid(W_g h), a gate per channel or one per head, before the output projection, which takes the
+residual in its epilogue. Value heads may have another size than key heads.
 """
 
 from __future__ import annotations
@@ -20,9 +22,12 @@ from .base import MIXERS, CacheNeed, Part, TensorSpec
 @MIXERS.register("gated_window_attention")
 class GatedWindowAttention(Part):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim, scale, window (0: all
-    keys), qk_norm_eps (None: q and k are not normed), unit_sink, output_gate (booleans),
-    position_encoding (a dict with its `kind` and `dims`, or None).
-    tensors: q, k, v, o (and g) matrices; q.norm, k.norm [head_dim]."""
+    keys), qk_norm_eps (None: q and k are not normed), qk_norm ("head", the default: per head with a
+    weight [head_dim] that the heads share; "whole": over the whole projection with weights [heads *
+    head_dim] and [kv_heads * head_dim]), unit_sink (bool), learned_sink (bool: a tensor `sink`
+    [heads]), output_gate (False, True or "channel": g [heads * value_dim, hidden]; "head": g [heads,
+    hidden]), position_encoding (a dict with its `kind` and `dims`, or None).
+    tensors: q, k, v, o (and g) matrices; q.norm, k.norm; sink."""
 
     @classmethod
     def _sizes(cls, spec: PartSpec):
@@ -37,10 +42,14 @@ class GatedWindowAttention(Part):
         heads, kv_heads, d, dv = cls._sizes(spec)
         rows = {"q": heads * d, "k": kv_heads * d, "v": kv_heads * dv}
         if p.get("output_gate"):
-            rows["g"] = heads * dv
+            rows["g"] = heads if p["output_gate"] == "head" else heads * dv
         out = [TensorSpec(spec.tensor_name(n), (r, hidden), "matrix") for n, r in rows.items()]
         if p.get("qk_norm_eps") is not None:
-            out += [TensorSpec(spec.tensor_name("q.norm"), (d,), "scale"), TensorSpec(spec.tensor_name("k.norm"), (d,), "scale")]
+            whole = p.get("qk_norm", "head") == "whole"
+            out += [TensorSpec(spec.tensor_name("q.norm"), (heads * d if whole else d,), "scale"),
+                    TensorSpec(spec.tensor_name("k.norm"), (kv_heads * d if whole else d,), "scale")]
+        if p.get("learned_sink"):
+            out.append(TensorSpec(spec.tensor_name("sink"), (heads,), "vector"))
         out.append(TensorSpec(spec.tensor_name("o"), (hidden, heads * dv), "matrix"))
         return out
 
@@ -66,6 +75,10 @@ class GatedWindowAttention(Part):
         self.window = int(p.get("window") or 0)
         self.norm_eps = p.get("qk_norm_eps")
         self.gated = bool(p.get("output_gate"))
+        self.gate_group = self.value_dim if p.get("output_gate") == "head" else 1
+        if p.get("qk_norm", "head") not in ("head", "whole"):
+            raise ValueError(f"gated_window_attention: qk_norm '{p.get('qk_norm')}' (head, whole)")
+        self.whole_norm = p.get("qk_norm", "head") == "whole"
         names = ("q", "k", "v") + (("g",) if self.gated else ())
         # One projection for q | k | v | g: the columns of its output in that order.
         self.in_weight = torch.cat([tensors.pop(spec.tensor_name(n)) for n in names], dim=0).contiguous()
@@ -74,6 +87,8 @@ class GatedWindowAttention(Part):
             self.q_norm, self.k_norm = tensors.pop(spec.tensor_name("q.norm")), tensors.pop(spec.tensor_name("k.norm"))
         # A sink whose logit is 0: one more term exp(0) in every head's denominator.
         self.sink = torch.zeros(self.num_heads, dtype=torch.float32, device=runtime.device) if p.get("unit_sink") else None
+        if p.get("learned_sink"):
+            self.sink = tensors.pop(spec.tensor_name("sink"))
         self.o_weight = tensors.pop(spec.tensor_name("o"))
         built = self.build_sub_parts(tensors)
         self.position_encoding = built[0] if built else None
@@ -91,11 +106,12 @@ class GatedWindowAttention(Part):
             proj, q_off=0, k_off=h * d, v_off=(h + g) * d, heads=h, kv_heads=g, q_dim=d, k_dim=d, value_dim=dv,
             q_norm=self.q_norm, k_norm=self.k_norm, q_span=d, k_span=d, eps=float(self.norm_eps or 0.0),
             table=table, interleaved=False, q_rot0=0, k_rot0=0, slots=group.slots if cache.writes else None,
-            keys=cache.keys, values=cache.values, page_size=cache.page_size, out_dtype=self.runtime.dtype)
+            keys=cache.keys, values=cache.values, page_size=cache.page_size, out_dtype=self.runtime.dtype, whole=self.whole_norm)
         out = ops.paged_attention_scored(
             q, cache.keys, cache.values, group.block_table, ctx.q_start, ctx.q_pos0, ctx.kv_len, h, g, d, dv,
             cache.page_size, ctx.max_q_len, self.scale, sink=self.sink, window=self.window,
             max_kv_len=ctx.max_kv_len, num_single=ctx.num_single)
         if self.gated:
-            out = ops.sigmoid_gate(out, proj, (h + g) * d + g * dv)
-        return ops.linear(out, self.o_weight, None, residual, out_dtype=residual.dtype)
+            out = ops.sigmoid_gate(out, proj, (h + g) * d + g * dv, group=self.gate_group)
+        # without a residual (a caller that sums by itself) the output leaves in float32
+        return ops.linear(out, self.o_weight, None, residual, out_dtype=residual.dtype if residual is not None else torch.float32)

@@ -124,8 +124,12 @@ class LatentAttention(Part):
             if self.own_latent:
                 ops.head_prep(proj, q_off=0, k_off=k_off, v_off=0, heads=0, kv_heads=1, slots=slots, **prep)
             query_latent = ops.rms_norm_columns(proj, 0, self.q_rank, self.query_norm, self.norm_eps, self.runtime.dtype)
-            queries = ops.linear(query_latent, self.uq_weight, None, None, out_dtype=torch.float32)
-            q = ops.head_prep(queries, q_off=0, k_off=0, v_off=0, heads=heads, kv_heads=0, slots=None, **prep)
+            if table is None:
+                # no channel turns: the queries leave their product in the engine's dtype
+                q = ops.linear(query_latent, self.uq_weight, None, None, out_dtype=self.runtime.dtype)
+            else:
+                queries = ops.linear(query_latent, self.uq_weight, None, None, out_dtype=torch.float32)
+                q = ops.head_prep(queries, q_off=0, k_off=0, v_off=0, heads=heads, kv_heads=0, slots=None, **prep)
         else:
             # queries [tokens, heads, d + r] with their rotated channels turned; the token's latent row into its page
             q = ops.head_prep(proj, q_off=0, k_off=k_off, v_off=0, heads=heads, kv_heads=1 if self.own_latent else 0,

@@ -86,3 +86,32 @@ class StreamRMSNorm(Part):
 
     def forward(self, ctx, x):
         return self.ops.streams_read_norm(x, self.read, self.weight, self.eps, self.streams, self.runtime.dtype)
+
+
+@NORMS.register("dynamic_tanh")
+class DynamicTanh(Part):
+    """A norm that computes no mean and no variance: tanh(alpha * x) * weight + bias, alpha one
+    learned scalar. params: size. tensors: weight [size], alpha [], bias [size]. x is a float32
+    stream (or a residual sum that is still pending: this norm's kernel makes it on the way); the
+    result is in the engine's dtype. As the norm AFTER a sublayer it is not run by itself:
+    `add_to` leaves x + mult * norm(y) pending, and the norm that reads the stream next makes
+    that sum and its own read in one pass."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
+        size = int(spec.params["size"])
+        return [TensorSpec(spec.tensor_name("weight"), (size,), "scale"), TensorSpec(spec.tensor_name("alpha"), (), "scale"),
+                TensorSpec(spec.tensor_name("bias"), (size,), "vector")]
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.weight = tensors[spec.tensor_name("weight")]
+        self.alpha = tensors[spec.tensor_name("alpha")].reshape(1)
+        self.bias = tensors[spec.tensor_name("bias")]
+
+    def forward(self, ctx, x):
+        return self.ops.dyt_norm(x, self.alpha, self.weight, self.bias, self.runtime.dtype)
+
+    def add_to(self, ctx, stream, y, mult: float):
+        """stream + mult * norm(y): float32, pending until the next read."""
+        return self.ops.residual_add(stream, y, mult, (self.alpha, self.weight, self.bias))
