@@ -324,6 +324,25 @@ def pukerax_config(size: dict, kv_rank: int = 512, rot_dim: int = 64, streams: i
             "layers": json.loads(json.dumps(layers))}
 
 
+def finezen_config(size: dict, window: int = 1024, kv_rank: int = 512, experts: int = 30, top: int = 6) -> dict:
+    """Finezen at the layer sizes of `size`: a windowed grouped-query attention (half of each head
+    rotated, ramped frequencies) and a windowed latent attention (the latent of Pukerax's, a query
+    latent of half the width) in turn; every feed-forward routes each token to `top` of `experts`
+    gated experts of an eighth of the dense width beside a gated shared expert of a quarter of it,
+    so that a token's feed-forward products are as many as a dense gated layer's. Every layer runs once."""
+    d = size["dim"]
+    mlp = {"kind": "moe", "expert": {"ff": size["ff"] // 8}, "router": {"experts": experts, "top": top}, "shared": {"ff": size["ff"] // 4}}
+    attention = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": size["heads"], "kv_heads": size["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": window},
+        "rot": {"base": 10000.0, "dims": d // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": size["heads"], "dim": d, "vdim": d, "kv_rank": kv_rank, "q_rank": size["width"] // 2, "scale": d ** -0.5,
+        "mask": {"size": window}}}
+    layers = [json.loads(json.dumps((attention, latent)[i % 2])) for i in range(size["layers"])]
+    return {"architecture": "Finezen", "vocab": size["vocab"], "width": size["width"], "embedding": {"scale": size["width"] ** 0.5},
+            "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": layers}
+
+
 def step_cache_bytes(cache, contexts) -> float:
     """Cache bytes that a decode step reads: per page group the keys and values a request can see
     (all of its context, or the window and the kept first keys), and every recurrent state
@@ -338,14 +357,17 @@ def step_cache_bytes(cache, contexts) -> float:
     return total
 
 
-def bidonex_beside_qwen2(torch, peak: dict, steps: int, warmup: int, sizes, with_zugarax: bool = False, pukerax: bool = False) -> dict:
+def bidonex_beside_qwen2(torch, peak: dict, steps: int, warmup: int, sizes, with_zugarax: bool = False, pukerax: bool = False,
+                         finezen: bool = False) -> dict:
     """Prefill and decode of the architectures at equal layer sizes; `with_zugarax` puts Zugarax
     in front of Bidonex (the closest of the others: a float32 stream, windows, a recurrent layer) and Qwen2;
-    `pukerax` times Pukerax beside Zugarax with latent attention in every layer (the closest to it) and Qwen2."""
+    `pukerax` times Pukerax beside Zugarax with latent attention in every layer (the closest to it) and Qwen2;
+    `finezen` times Finezen beside Pukerax (the closest to it: a float32 stream, latent attention with a query
+    latent and head gates, routed experts with a shared one) and Qwen2."""
     from paged_attention_engine_b200.engine.llm import Engine
     from paged_attention_engine_b200.sampling import SamplingRow
 
-    out: dict = {"only": "pukerax" if pukerax else "zugarax" if with_zugarax else "bidonex", "peaks": peak["source"], "sizes": {}}
+    out: dict = {"only": "finezen" if finezen else "pukerax" if pukerax else "zugarax" if with_zugarax else "bidonex", "peaks": peak["source"], "sizes": {}}
     for name in sizes:
         bidonex, qwen = bidonex_pair(BIDONEX_SIZES[name])
         rows: dict = {}
@@ -353,6 +375,8 @@ def bidonex_beside_qwen2(torch, peak: dict, steps: int, warmup: int, sizes, with
         archs = archs + (("bidonex", bidonex), ("qwen2", qwen))
         if pukerax:
             archs = (("pukerax", pukerax_config(BIDONEX_SIZES[name])), ("zugarax_latent", zugarax_latent_config(BIDONEX_SIZES[name])), ("qwen2", qwen))
+        if finezen:
+            archs = (("finezen", finezen_config(BIDONEX_SIZES[name])), ("pukerax", pukerax_config(BIDONEX_SIZES[name])), ("qwen2", qwen))
         for arch, raw in archs:
             engine = Engine.from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
             row: dict = {"layers": BIDONEX_SIZES[name]["layers"], "weight_gb": round(engine.weight_bytes() / 1e9, 3)}
@@ -787,9 +811,9 @@ def main() -> int:
                         help="layer sizes for --only decode / prefill (the headline line is always the 1.5B shape)")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context length for --only decode")
     parser.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
-    parser.add_argument("--arch", choices=("qwen2", "bidonex", "zugarax", "zugarax_latent", "pukerax"), default="qwen2",
+    parser.add_argument("--arch", choices=("qwen2", "bidonex", "zugarax", "zugarax_latent", "pukerax", "finezen"), default="qwen2",
                         help="with --only decode / prefill: the architecture that runs at the --shape's layer sizes")
-    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b", "bidonex", "zugarax", "pukerax"), default="all",
+    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b", "bidonex", "zugarax", "pukerax", "finezen"), default="all",
                         help="time one part only (for profiling); the JSON line then holds that part alone")
     args = parser.parse_args()
 
@@ -818,10 +842,10 @@ def main() -> int:
     if args.only == "pressure32b":
         print(json.dumps(pressure_32b(torch, args.layers_32b)))
         return 0
-    if args.only in ("bidonex", "zugarax", "pukerax"):
+    if args.only in ("bidonex", "zugarax", "pukerax", "finezen"):
         sizes = ("1.5b", "7b") if args.shape == "1.5b" else (args.shape,)
         print(json.dumps(bidonex_beside_qwen2(torch, peak, args.steps, warmup, sizes, with_zugarax=args.only == "zugarax",
-                                              pukerax=args.only == "pukerax")))
+                                              pukerax=args.only == "pukerax", finezen=args.only == "finezen")))
         return 0
     if args.only == "products":
         for row in time_products({"1.5b": MODEL, "7b": MODEL_7B, "32b": MODEL_32B}[args.shape], args.batch, torch, peak):
@@ -841,7 +865,7 @@ def main() -> int:
             size["layers"] = args.layers
         args.layers = size["layers"]
         bidonex, model = bidonex_pair(size)
-        raw = {"zugarax": zugarax_config, "zugarax_latent": zugarax_latent_config, "pukerax": pukerax_config}.get(args.arch, lambda size: bidonex)(size)
+        raw = {"zugarax": zugarax_config, "zugarax_latent": zugarax_latent_config, "pukerax": pukerax_config, "finezen": finezen_config}.get(args.arch, lambda size: bidonex)(size)
         engine = Engine.from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
     else:
         engine = Engine.from_random(model, seed=0, dtype="bfloat16", device="cuda:0")

@@ -1,4 +1,4 @@
-// Causal attention of many query heads over ONE key/value head whose value is the leading DV
+// Causal attention (with an optional sliding window) of many query heads over ONE key/value head whose value is the leading DV
 // channels of its key row (latent attention with the expansions folded into the queries and the
 // output: a key row is [latent | shared rotated part], D channels, and the latent is also the
 // value), for bfloat16 on tensor cores (mma.sync m16n8k16, float32 accumulation). D may be large
@@ -20,7 +20,9 @@
 //
 // A single token's keys are shared out over `splits` blocks that leave unnormalised partial
 // results in scratch; `merge` adds them up in their order. Scores and the softmax are float32.
-// Keys are folded in ascending order; a query's result depends on its own keys only.
+// Keys are folded in ascending order; a query's result depends on its own keys only. With a
+// window w a query at position i sees the keys i - w < j <= i: a block starts at the tile of its
+// first row's first key, and keys before that key are not fetched (their pages may be gone).
 #include "attention_mma.cuh"
 
 using namespace pae;
@@ -46,6 +48,7 @@ struct LatentParams {
   int table_width, heads, page_size, D, DV, cols;
   float scale;
   int splits;
+  int window;                   // 0: every earlier key
   float* part_out;              // [requests, heads, splits, DV]
   float* part_max;              // [requests, heads, splits]  (in units of log 2)
   float* part_sum;
@@ -65,6 +68,7 @@ __global__ void __launch_bounds__(THREADS) latent_kernel(const LatentParams p) {
   const int rows = single ? min(ROWS, p.heads - head0) : min(ROWS, q_count - tile * ROWS);
   const int pos0 = p.q_pos0[b] + tile * ROWS;
   const int kv_end = single ? min(p.kv_len[b], pos0 + 1) : min(p.kv_len[b], pos0 + rows);
+  const int kv_begin = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;      // the first key that the block's first row sees
   const int D = p.D, DV = p.DV;
   const int chunks = D >> 3;                                           // 16-byte chunks of a row
   const int row_bytes = D * 2 + 16;
@@ -90,7 +94,7 @@ __global__ void __launch_bounds__(THREADS) latent_kernel(const LatentParams p) {
   auto fetch = [&](int stage, int key0) {
     const int key = key0 + f_row;
     uint8_t* dst = k_stage + (size_t)stage * TILE * row_bytes + f_row * row_bytes;
-    if (key < kv_end) {
+    if (key < kv_end && key >= kv_begin) {
       const int index = key / p.page_size;
       const int page = checked_page(table[checked_table_index(index, p.table_width)]);
       const __nv_bfloat16* src = p.keys + ((size_t)page * p.page_size + (key - index * p.page_size)) * D;
@@ -114,11 +118,11 @@ __global__ void __launch_bounds__(THREADS) latent_kernel(const LatentParams p) {
   const float scale2 = p.scale * LOG2E;
   const int col0 = warp * p.cols;                                      // this warp's first value column
 
-  const int tiles = (kv_end + TILE - 1) / TILE;
-  int t_begin = 0, t_end = tiles;
+  const int tiles = (kv_end + TILE - 1) / TILE, tile0 = kv_begin / TILE;
+  int t_begin = tile0, t_end = tiles;
   if (single) {
-    const int each = (tiles + p.splits - 1) / p.splits;
-    t_begin = min(tiles, split * each);
+    const int each = (tiles - tile0 + p.splits - 1) / p.splits;
+    t_begin = min(tiles, tile0 + split * each);
     t_end = min(tiles, t_begin + each);
   }
   if (t_begin < t_end) fetch(t_begin & 1, t_begin * TILE);
@@ -176,7 +180,8 @@ __global__ void __launch_bounds__(THREADS) latent_kernel(const LatentParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int half = j >> 1, key = key0 + i * 8 + c2 + (j & 1);
-          s[i][j] = (key < kv_end && key <= my_pos[half]) ? s[i][j] * scale2 : -FLT_MAX;
+          const bool seen = key < kv_end && key <= my_pos[half] && (p.window <= 0 || key + p.window > my_pos[half]);
+          s[i][j] = seen ? s[i][j] * scale2 : -FLT_MAX;
           block_max[half] = fmaxf(block_max[half], s[i][j]);
         }
       float rescale[2];
@@ -308,11 +313,12 @@ PAE_EXPORT int pae_attention_latent_mma_supports(int d, int dv) {
 
 // bfloat16. out [tokens, heads, dv]; q [tokens, heads, d]; keys [pages, 1, page_size, d]. With `scratch`
 // (seqs * heads * splits * (dv + 2) floats) a request that brings ONE token is taken by blocks of up to 32
-// heads each, its keys shared out over `splits` blocks and merged by a second kernel.
+// heads each, its keys shared out over `splits` blocks and merged by a second kernel. window: 0, or how many keys
+// (itself included) a query sees.
 PAE_EXPORT int pae_paged_attention_latent_mma(void* out, const void* q, const void* keys, const int* block_table,
                                               int table_width, const int* q_start, const int* q_pos0, const int* kv_len,
                                               int seqs, int max_q_len, int heads, int d, int dv, int page_size, float scale,
-                                              int splits, float* scratch, void* stream) {
+                                              int window, int splits, float* scratch, void* stream) {
   if (seqs == 0 || max_q_len == 0) return 0;
   if (!pae_attention_latent_mma_supports(d, dv)) return fail(2, "paged_attention_latent_mma: key rows of %d channels with values of %d", d, dv);
   if (splits < 1 || (scratch == nullptr && splits != 1)) return fail(2, "paged_attention_latent_mma: %d splits", splits);
@@ -322,7 +328,7 @@ PAE_EXPORT int pae_paged_attention_latent_mma(void* out, const void* q, const vo
     return fail(2, "paged_attention_latent_mma: an operand does not start on a 16-byte boundary");
   const int cols = (((dv + 3) / 4) + 15) / 16 * 16;
   LatentParams p{(__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)keys, block_table, q_start, q_pos0, kv_len,
-                 table_width, heads, page_size, d, dv, cols, scale, splits, nullptr, nullptr, nullptr};
+                 table_width, heads, page_size, d, dv, cols, scale, splits, window < 0 ? 0 : window, nullptr, nullptr, nullptr};
   if (scratch != nullptr) {
     const size_t units = (size_t)seqs * heads * splits;
     p.part_out = scratch;

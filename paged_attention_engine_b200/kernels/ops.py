@@ -1232,7 +1232,7 @@ def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len
         raise KernelError(f"paged_attention_scored: q rows of {q.shape[1]} for {num_heads} heads of {head_dim}")
     out = torch.empty((tokens, num_heads * value_dim), dtype=q.dtype, device=q.device)
     in_keys = values.data_ptr() == keys.data_ptr()        # a key row's leading channels are its value
-    if (in_keys and q.dtype == torch.bfloat16 and use_tensor_cores and form != "simt" and num_kv_heads == 1 and not window
+    if (in_keys and q.dtype == torch.bfloat16 and use_tensor_cores and form != "simt" and num_kv_heads == 1 and not keep_first
             and not softcap and temp is None and r1 is None and sink is None):
         # Many heads over one latent key/value head (csrc/attention_latent_mma.cu). A request that brings one
         # token is blocks of up to 32 heads; its keys are shared out (two tiles of 64 a block at least) until the launch fills the GPU once.
@@ -1243,11 +1243,12 @@ def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len
             splits, scratch = 1, None
             if num_single is None or num_single > 0:
                 groups = -(-num_heads // 32)
-                splits = max(1, min(-(-(max_kv_len or 0) // 128), _sm_count(q.device) // max(1, seqs * groups)))
+                reach = min(max_kv_len or 0, window + 63) if window else (max_kv_len or 0)       # a window's keys and the tile they start in
+                splits = max(1, min(-(-reach // 128), _sm_count(q.device) // max(1, seqs * groups)))
                 scratch = torch.empty(seqs * num_heads * splits * (value_dim + 2), dtype=torch.float32, device=q.device)
             _check(lib, lib.pae_paged_attention_latent_mma(
                 _ptr(out), _ptr(q), _ptr(keys), _ptr(block_table), block_table.shape[1], _ptr(q_start), _ptr(q_pos0), _ptr(kv_len),
-                seqs, max_q_len, num_heads, head_dim, value_dim, page_size, scale, splits, _ptr(scratch), _stream()),
+                seqs, max_q_len, num_heads, head_dim, value_dim, page_size, scale, int(window or 0), splits, _ptr(scratch), _stream()),
                 2 if scratch is not None else 1)
             return out
     if (q.dtype == torch.bfloat16 and use_tensor_cores and head_dim in (32, 64, 128) and value_dim in (32, 64, 128)

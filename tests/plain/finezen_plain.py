@@ -84,16 +84,19 @@ def windowed_softmax_attention(q, k, v, scale, window, sink=None):
     exp(sink_h) in the denominator, with no value."""
     T, H = q.shape[0], q.shape[1]
     per = H // k.shape[1]
+    k, v = k.repeat_interleave(per, dim=1), v.repeat_interleave(per, dim=1)      # every query head's own copy
     out = torch.zeros(T, H, v.shape[2], dtype=F)
     for i in range(T):
         first = max(0, i - window + 1) if window else 0
-        for h in range(H):
-            g = h // per
-            scores = (k[first: i + 1, g] @ q[i, h]) * scale
-            top = scores.max() if sink is None else torch.maximum(scores.max(), sink[h])
-            e = torch.exp(scores - top)
-            denominator = e.sum() + (torch.exp(sink[h] - top) if sink is not None else 0.0)
-            out[i, h] = (e / denominator) @ v[first: i + 1, g]
+        scores = torch.einsum("hn,jhn->hj", q[i], k[first: i + 1]) * scale
+        top = scores.max(dim=1, keepdim=True).values
+        if sink is not None:
+            top = torch.maximum(top, sink[:, None])
+        e = torch.exp(scores - top)
+        denominator = e.sum(dim=1, keepdim=True)
+        if sink is not None:
+            denominator = denominator + torch.exp(sink[:, None] - top)
+        out[i] = torch.einsum("hj,jhv->hv", e / denominator, v[first: i + 1])
     return out
 
 
@@ -143,14 +146,14 @@ def gated_expert(h, tensors, prefix):
 
 def route(h, router, top, margins=None):
     """Per token the `top` experts with the largest sigmoid(W_router h) and those scores, which are
-    the weights as they are. `margins`, a list, receives per token how far the last chosen score is
-    from the first one not chosen."""
-    scores = torch.sigmoid(h @ _f(router).T)
-    best = scores.topk(min(top + 1, scores.shape[1]), dim=-1)
+    the weights as they are. `margins`, a list, receives per token how far the last chosen expert's
+    logit is from that of the first one not chosen."""
+    logits = h @ _f(router).T
+    best = logits.topk(min(top + 1, logits.shape[1]), dim=-1)
     if margins is not None:
-        margins.append(best.values[:, top - 1] - best.values[:, top] if scores.shape[1] > top
+        margins.append(best.values[:, top - 1] - best.values[:, top] if logits.shape[1] > top
                        else torch.full((h.shape[0],), math.inf, dtype=F))
-    return best.indices[:, :top], best.values[:, :top]
+    return best.indices[:, :top], torch.sigmoid(best.values[:, :top])
 
 
 def mixture(h, tensors, prefix, mlp, margins=None):
