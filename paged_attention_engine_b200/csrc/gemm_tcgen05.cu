@@ -673,7 +673,7 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
           tmem_load16(lane_address + c0, gate);
           tmem_load16(lane_address + c0 + 16, up);
           const int col0 = tile_b * PBN + c0;
-          if (row < p.rows_a && col0 < p.rows_b) store_swiglu_chunk(p, row, col0, gate, up);
+          if (row < rows_end && col0 < p.rows_b) store_swiglu_chunk(p, row, col0, gate, up);
         }
       } else {
 #pragma unroll 1
@@ -897,6 +897,29 @@ PAE_EXPORT int pae_linear_grouped_tcgen05(void* out, const void* x, const void* 
   p.kb_per_split = p.k_blocks;
   p.ld_out = n;
   p.out_f32 = out_f32;
+  p.group_tiles = tiles;
+  p.groups = groups;
+  p.error = error;
+  return launch_persistent(p, x, w, k, (cudaStream_t)stream);
+}
+
+// The grouped product with SiLU x up in its epilogue: every matrix of w is [n, k] with 16 gate rows,
+// their 16 up rows, and so on; out [max_tiles * 128, n / 2] bfloat16 = silu(gate) * up, gate and up rounded
+// to bfloat16 first, as the grouped product followed by the stand-alone kernel leaves them. n is a multiple of 32.
+PAE_EXPORT int pae_linear_grouped_swiglu_tcgen05(void* out, const void* x, const void* w, const int* tiles, int max_tiles, int groups,
+                                                 int n, int k, int* error, void* stream) {
+  if (max_tiles == 0 || n == 0 || groups == 0) return 0;
+  if (int err = check_operands(x, w, k)) return err;
+  if (n % 32) return fail(2, "linear_grouped_swiglu_tcgen05: %d columns are not a multiple of 32", n);
+  if ((long long)groups * n > 0x7fffffffLL) return fail(2, "linear_grouped_swiglu_tcgen05: %d matrices of %d rows", groups, n);
+  Params p{};
+  p.out = out;
+  p.rows_a = max_tiles * BM;
+  p.rows_b = n;
+  p.k_blocks = (k + BK - 1) / BK;
+  p.kb_per_split = p.k_blocks;
+  p.ld_out = n / 2;
+  p.swiglu = 1;
   p.group_tiles = tiles;
   p.groups = groups;
   p.error = error;

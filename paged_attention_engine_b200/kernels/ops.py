@@ -1566,16 +1566,29 @@ def expert_plan(x, chosen, experts: int, input_weights=None) -> ExpertPlan:
     return ExpertPlan(staged, tiles, rows, experts)
 
 
-def linear_grouped(x, weight, plan: ExpertPlan, out_dtype=None, activation: str | None = None) -> torch.Tensor:
+def linear_grouped(x, weight, plan: ExpertPlan, out_dtype=None, activation: str | None = None, swiglu_block: int | None = None) -> torch.Tensor:
     """out[row] = act(x[row] . weight[g(row)]^T) for the rows of the plan's tiles: x [max_tiles *
     tile, K] sorted by expert, weight [experts, N, K]. Rows that are no pair keep what the fresh
-    output held. The tcgen05 kernel walks the tiles as it walks a plain product's (bfloat16, K a
-    multiple of 8); everything else, float32 above all, takes the CUDA-core kernel."""
+    output held (or hold anything). The tcgen05 kernel walks the tiles as it walks a plain product's (bfloat16, K a
+    multiple of 8); everything else, float32 above all, takes the CUDA-core kernel. `swiglu_block`
+    (0: an expert's rows [0, N/2) are its gate and [N/2, N) its up projection; 16: blocks of 16 gate
+    rows and their 16 up rows, the layout of `interleave_gate_up`): the result is silu(gate) * up,
+    [rows, N / 2] in x's dtype, in the tcgen05 product's epilogue for blocks of 16, else by `silu_mul`."""
     _need(x, "linear_grouped: x")
     _need(weight, "linear_grouped: weight", x.dtype)
     experts, n, k = weight.shape
     if x.shape[1] != k or experts != plan.experts or x.shape[0] != plan.max_tiles * EXPERT_TILE:
         raise KernelError(f"linear_grouped: x {tuple(x.shape)}, weight {tuple(weight.shape)}, {plan.max_tiles} tiles of {plan.experts} experts")
+    if swiglu_block is not None:
+        if activation is not None or out_dtype not in (None, x.dtype):
+            raise KernelError("linear_grouped: SiLU x up leaves the operands' dtype and takes no other activation")
+        if swiglu_block == SWIGLU_BLOCK and n % 32 == 0 and _tensor_core_shape(x, weight, None, x.dtype):
+            out = torch.empty((x.shape[0], n // 2), dtype=x.dtype, device=x.device)
+            lib = _lib("gemm_tcgen05")
+            _check(lib, lib.pae_linear_grouped_swiglu_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(plan.tiles), plan.max_tiles, experts,
+                                                              n, k, _ptr(_error_flag(x.device)), _stream()))
+            return out
+        return silu_mul(linear_grouped(x, weight, plan), swiglu_block)
     out_dtype = out_dtype or x.dtype
     out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
     max_tiles = plan.max_tiles

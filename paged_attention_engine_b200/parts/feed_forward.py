@@ -192,9 +192,18 @@ class RoutedExperts(Part):
             self.router = torch.cat([self.router, tensors.pop(name("shared.sg"))], dim=0).contiguous()
         self.correction = tensors.pop(name("correction")) if p.get("choice_correction") else None
         ups = [tensors.pop(name(f"e{e}.up")) for e in range(self.experts)]
+        self.gate_up_block = 0
         if self.gated:
-            # gate rows, then up rows: one grouped product, SiLU x up after it
-            ups = [torch.cat([tensors.pop(name(f"e{e}.gate")), ups[e]], dim=0) for e in range(self.experts)]
+            # Gate and up are one grouped product. Where the kernels offer it, an expert's rows alternate
+            # in blocks (16 gate rows, their 16 up rows, ...) so that SiLU x up runs inside the product;
+            # else an expert's gate rows come first and its up rows after them.
+            gates = [tensors.pop(name(f"e{e}.gate")) for e in range(self.experts)]
+            interleave = getattr(self.ops, "interleave_gate_up", None)
+            mixed = [interleave(g, u) for g, u in zip(gates, ups)] if interleave is not None else [None]
+            if mixed[0] is not None:
+                ups, self.gate_up_block = mixed, int(getattr(self.ops, "SWIGLU_BLOCK", 16))
+            else:
+                ups = [torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]
         downs = [tensors.pop(name(f"e{e}.down")) for e in range(self.experts)]
         self.up_weight = torch.stack(ups, dim=0).contiguous()            # [experts, ff or 2 ff, hidden]
         self.down_weight = torch.stack(downs, dim=0).contiguous()        # [experts, hidden, ff]
@@ -241,9 +250,10 @@ class RoutedExperts(Part):
         if self.shared:
             base = ops.linear(self._shared_hidden(x), self.shared_down, None, residual, out_dtype=torch.float32)
         plan = ops.expert_plan(x, chosen, self.experts, weights if self.weight_on_input else None)
-        hidden = ops.linear_grouped(plan.staged, self.up_weight, plan, activation=self.activation)
         if self.gated:
-            hidden = ops.silu_mul(hidden)
+            hidden = ops.linear_grouped(plan.staged, self.up_weight, plan, swiglu_block=self.gate_up_block)
+        else:
+            hidden = ops.linear_grouped(plan.staged, self.up_weight, plan, activation=self.activation)
         y = ops.linear_grouped(hidden, self.down_weight, plan, out_dtype=torch.float32)
         return ops.expert_combine(y, plan, None if self.weight_on_input else weights, x, base,
                                   base_gate=(logits, self.router_rows) if self.shared_gate else None)
