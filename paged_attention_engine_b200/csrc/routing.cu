@@ -195,6 +195,24 @@ __global__ void __launch_bounds__(256) expert_tiles_kernel(int* __restrict__ fir
   }
 }
 
+// dst[c] = w * src[c] for c < width, a float32 product rounded once; 16 bytes a step where both rows allow it.
+template <typename T>
+__device__ __forceinline__ void scaled_row(T* __restrict__ dst, const T* __restrict__ src, float w, int width, int lane, int lanes) {
+  constexpr int PER = 16 / (int)sizeof(T);
+  if ((width % PER) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+    for (int c = lane; c < width / PER; c += lanes) {
+      int4 in = ((const int4*)src)[c], out;
+      const T* a = (const T*)&in;
+      T* b = (T*)&out;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) b[j] = from_float<T>(w * to_float(a[j]));
+      ((int4*)dst)[c] = out;
+    }
+  } else {
+    for (int c = lane; c < width; c += lanes) dst[c] = from_float<T>(w * to_float(src[c]));
+  }
+}
+
 // One block per pair: its row is its expert's first row plus its rank; the token's input goes there.
 template <typename T>
 __global__ void __launch_bounds__(128) expert_gather_kernel(T* __restrict__ staged, int* __restrict__ rows, const T* __restrict__ x,
@@ -214,8 +232,7 @@ __global__ void __launch_bounds__(128) expert_gather_kernel(T* __restrict__ stag
   const T* src = x + (size_t)(i / top) * width;
   T* dst = staged + (size_t)row * width;
   if (scale != nullptr) {                               // an expert that is weighted on its input
-    const float w = scale[i];
-    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = from_float<T>(w * to_float(src[c]));
+    scaled_row(dst, src, scale[i], width, (int)threadIdx.x, (int)blockDim.x);
   } else if (((sizeof(T) * width) & 15) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
     const int n = (int)(sizeof(T) * width / 16);
     for (int c = threadIdx.x; c < n; c += blockDim.x) ((int4*)dst)[c] = ((const int4*)src)[c];
@@ -287,8 +304,7 @@ __global__ void __launch_bounds__(SMALL_THREADS) expert_plan_small_kernel(int* _
     const T* src = x + (size_t)(i / top) * width;
     T* dst = staged + (size_t)row * width;
     if (scale != nullptr) {
-      const float w = scale[i];
-      for (int c = lane; c < width; c += 32) dst[c] = from_float<T>(w * to_float(src[c]));
+      scaled_row(dst, src, scale[i], width, lane, 32);
     } else if (((sizeof(T) * width) & 15) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
       const int n16 = (int)(sizeof(T) * width / 16);
       for (int c = lane; c < n16; c += 32) ((int4*)dst)[c] = ((const int4*)src)[c];
