@@ -344,6 +344,48 @@ __global__ void expert_combine_kernel(float* __restrict__ out, const float* __re
   out[i] = acc;
 }
 
+// The same sum, four neighbouring columns a thread (width a multiple of 4, float32 rows 16-byte aligned): a
+// quarter of the row and weight look-ups and of the gate's exponentials, 16-byte loads and stores.
+template <typename T>
+__global__ void expert_combine4_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ rows,
+                                       const float* __restrict__ weights, const T* __restrict__ x, const float* __restrict__ base,
+                                       int base_planes, const float* __restrict__ gate, int gate_planes, int gate_ld, int gate_col,
+                                       long long tokens, int top, int width, long long total) {
+  dependent_launch_prologue();
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= total) return;
+  const long long t = i / width;
+  const int c = (int)(i - t * width);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (base != nullptr)
+    for (int k = 0; k < base_planes; ++k) {
+      const float4 b = *(const float4*)(base + (size_t)k * total + i);
+      acc[0] += b.x, acc[1] += b.y, acc[2] += b.z, acc[3] += b.w;
+    }
+  if (gate != nullptr) {
+    float g = 0.f;
+    for (int k = 0; k < gate_planes; ++k) g += gate[((size_t)k * tokens + t) * gate_ld + gate_col];
+    const float open = 1.f + expf(-g);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = acc[j] / open;
+  }
+  for (int k = 0; k < top; ++k) {
+    const int row = rows[t * top + k];
+    const float w = weights != nullptr ? weights[t * top + k] : 1.f;
+    float v[4];
+    if (row >= 0) {
+      const float4 r = *(const float4*)(y + (size_t)row * width + c);
+      v[0] = r.x, v[1] = r.y, v[2] = r.z, v[3] = r.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = to_float(x[i + j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] += w * v[j];
+  }
+  *(float4*)(out + i) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
 }  // namespace
 
 PAE_EXPORT int pae_route(int* chosen, float* weights, float* dense, const float* logits, int splits, int ld, const float* correction, int tokens,
@@ -411,8 +453,15 @@ PAE_EXPORT int pae_expert_combine(float* out, const float* y, const int* rows, c
                                   int width, int dtype, void* stream) {
   const long long total = (long long)tokens * width;
   if (total == 0) return 0;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype != kF32 && dtype != kBF16) return fail(1, "expert_combine: unknown dtype %d", dtype);
+  if (width % 4 == 0 && ((((uintptr_t)out) | ((uintptr_t)y) | ((uintptr_t)base)) & 15) == 0) {
+    const unsigned blocks4 = (unsigned)((total / 4 + 255) / 256);
+    if (dtype == kF32) launch_kernel(expert_combine4_kernel<float>, blocks4, 256, 0, s, out, y, rows, weights, (const float*)x, base, base_planes, gate, gate_planes, gate_ld, gate_col, (long long)tokens, top, width, total);
+    else launch_kernel(expert_combine4_kernel<__nv_bfloat16>, blocks4, 256, 0, s, out, y, rows, weights, (const __nv_bfloat16*)x, base, base_planes, gate, gate_planes, gate_ld, gate_col, (long long)tokens, top, width, total);
+    return check_launch("expert_combine");
+  }
+  const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == kF32) launch_kernel(expert_combine_kernel<float>, blocks, 256, 0, s, out, y, rows, weights, (const float*)x, base, base_planes, gate, gate_planes, gate_ld, gate_col, (long long)tokens, top, width, total);
   else if (dtype == kBF16) launch_kernel(expert_combine_kernel<__nv_bfloat16>, blocks, 256, 0, s, out, y, rows, weights, (const __nv_bfloat16*)x, base, base_planes, gate, gate_planes, gate_ld, gate_col, (long long)tokens, top, width, total);
   else return fail(1, "expert_combine: unknown dtype %d", dtype);

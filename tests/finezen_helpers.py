@@ -69,8 +69,9 @@ SMALL_B = config(257, 128, [
     layer(latent(4, 32, 32, 64, 48, 0.18, window=24), moe(128, 4, 2, shared=64)),
     layer(attention(2, 2, 128, 128, 0.09, window=16, rot=rot(128, 500000.0)), moe(64, 7, 3)),
 ], scale=1.0, mult=1.0, loop=(0, 3, 2), eps=1e-6)
-# No loop; one head; a window of one (a token sees itself only) and of two; everything rotated.
-NO_LOOP = config(97, 48, [
+# No loop; one head; a window of one (a token sees itself only) and of two; everything rotated; a
+# width that is no multiple of 8 (no tensor-core product takes it).
+NO_LOOP = config(97, 52, [
     layer(attention(1, 1, 8, 8, 0.4, window=1, rot=rot(8, 100.0)), moe(32, 3, 1, shared=16)),
     layer(latent(1, 8, 16, 24, 32, 0.3, window=2), moe(16, 2, 2)),
     layer(attention(3, 1, 8, 24, 0.35, window=50, rot=rot(4, 30.0, (2.0, 16, 4.0, 1.0))), None),
