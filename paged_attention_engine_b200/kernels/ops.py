@@ -1234,7 +1234,7 @@ def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len
     in_keys = values.data_ptr() == keys.data_ptr()        # a key row's leading channels are its value
     if (in_keys and q.dtype == torch.bfloat16 and use_tensor_cores and form != "simt" and num_kv_heads == 1 and not keep_first
             and not softcap and temp is None and r1 is None and sink is None):
-        # Many heads over one latent key/value head (csrc/attention_latent_mma.cu). A request that brings one
+        # Many heads over one latent key/value head, causal or windowed (csrc/attention_latent_mma.cu). A request that brings one
         # token is blocks of up to 32 heads; its keys are shared out (two tiles of 64 a block at least) until the launch fills the GPU once.
         lib = _lib("attention_latent_mma")
         if lib.pae_attention_latent_mma_supports(head_dim, value_dim):

@@ -12,6 +12,9 @@ one key/value head whose key is [c | shared] and whose value is c; the value exp
 is applied to the attention's output over the latent. A layer may read the latent of an
 earlier layer (through the schedule's `cache_from`): it has no down projection and writes nothing.
 
+With `rot_dim` 0 and no position encoding there is no shared part and nothing turns: the key row
+is the latent alone. With a `window` a query sees that many keys, itself included.
+
 Two options. The queries may go through a latent of their own: c_q = RMSnorm(W_dq h) with a
 weight, q = W_uq c_q (`q_rank`). And every head's output may be multiplied by one sigmoid of a
 projection of h (`head_gate`, a gate per head, not per channel) before the output projection.

@@ -174,6 +174,52 @@ def test_gated_experts_weighted_on_their_input(dtype, tokens, top, experts, widt
         _close(fused[pairs], hidden[pairs].double().cpu(), dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, d, dv, window, page, requests", [
+    (4, 64, 64, 24, 16, [(0, 70)]),                                   # a prompt from its first token, past the window
+    (3, 32, 16, 100, 16, [(150, 1), (37, 40), (200, 1), (0, 1)]),     # single tokens far in, a portion, a first token
+    (33, 48, 48, 1, 8, [(20, 3), (64, 1)]),                           # more heads than a block's rows; a window of one
+    (2, 288, 288, 65, 32, [(130, 2), (63, 66)]),                      # a wide latent; windows that end at and beside tile borders
+    (5, 20, 12, 30, 4, [(90, 1), (10, 50)]),                          # sizes that only the CUDA-core kernel takes
+])
+def test_windowed_attention_over_latent_rows(dtype, heads, d, dv, window, page, requests):
+    """Many heads over ONE cached row per token whose leading channels are its value, with a
+    window: prompts, portions and single tokens in one step, over a shuffled block table whose
+    entries before every window are gone (-1) and whose pool holds NaN in every page that no request holds."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(heads * d + window)
+    scale = 0.6 / d ** 0.5
+    total_pages = sum(-(-(past + new) // page) for past, new in requests) + 3
+    order = torch.randperm(total_pages, generator=gen).tolist()
+    pool = torch.full((total_pages, 1, page, d), float("nan"))
+    width = max(-(-(past + new) // page) for past, new in requests)
+    table = torch.full((len(requests), width), -1, dtype=torch.int32)
+    q_rows, want_rows, q_start, q_pos0, kv_len = [], [], [0], [], []
+    for b, (past, new) in enumerate(requests):
+        n = past + new
+        rows = torch.randn(n, 1, d, generator=gen).to(dtype).double()
+        q = torch.randn(n, heads, d, generator=gen).to(dtype).double()
+        want_rows.append(plain.windowed_softmax_attention(q, rows, rows[:, :, :dv], scale, window)[past:])
+        q_rows.append(q[past:])
+        first_seen = max(0, past - window + 1)
+        for index in range(first_seen // page, -(-n // page)):
+            table[b, index] = order.pop()
+        for pos in range(first_seen // page * page, n):  # pages that no query of the step sees stay NaN
+            pool[table[b, pos // page], 0, pos % page] = rows[pos, 0].float()
+        q_start.append(q_start[-1] + new)
+        q_pos0.append(past)
+        kv_len.append(n)
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)
+    keys = dev(pool.to(dtype))
+    singles = sum(1 for _, new in requests if new == 1)
+    got = ops.paged_attention_scored(
+        dev(torch.cat(q_rows).to(dtype).view(-1, heads * d)), keys, keys, dev(table), ints(q_start), ints(q_pos0), ints(kv_len), heads, 1,
+        d, dv, page, max(new for _, new in requests), scale, window=window, max_kv_len=max(kv_len), num_single=singles)
+    want = torch.cat(want_rows).view(-1, heads * dv)
+    assert bool(torch.isfinite(got).all())
+    _close(got, want, dtype)
+
+
 # --------------------------------------------------------------------------- #
 # Single parts of a model against the plain functions
 # --------------------------------------------------------------------------- #
