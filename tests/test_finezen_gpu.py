@@ -75,7 +75,7 @@ def test_norm_without_statistics_alone_and_with_the_sum_before_it(dtype, tokens,
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, kv_heads, d, dv, dims, tokens", [(4, 2, 12, 20, 8, 5), (8, 1, 128, 80, 32, 70), (3, 3, 10, 6, 10, 9), (1, 1, 8, 8, 0, 3)])
+@pytest.mark.parametrize("heads, kv_heads, d, dv, dims, tokens", [(4, 2, 12, 20, 8, 5), (6, 2, 128, 96, 64, 70), (3, 3, 10, 6, 10, 9), (1, 1, 8, 8, 0, 3)])
 def test_query_and_key_norm_over_the_whole_projection(dtype, heads, kv_heads, d, dv, dims, tokens):
     """One RMS norm over all query heads of a token and one over all its key heads, weights as long
     as the projections, then the rotation of each head's leading span, against the plain functions."""
