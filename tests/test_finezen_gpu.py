@@ -314,6 +314,28 @@ def test_long_decoding_past_every_window(folders, dtype):
     _check(folders["small_b"], dtype, helpers.trace_tail(requests, tail=140), requests, oracle, page)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_long_prompt_over_many_pages(tmp_path, dtype):
+    """400 tokens over 25 pages, windows of 130 and 100 keys that pass over prompt and decoded
+    tokens alike, both layers run twice; every expert is chosen, so no router's choice can be a
+    close call. Head sizes that the tensor-core attention kernels take in bfloat16."""
+    raw = fh.config(131, 64, [
+        fh.layer(fh.attention(4, 2, 32, 32, 0.18, window=130, rot=fh.rot(16, 10000.0, (4.0, 64, 16.0, 1.0))), fh.moe(32, 3, 3, shared=48)),
+        fh.layer(fh.latent(4, 16, 32, 48, 40, 0.25, window=100), fh.moe(48, 2, 2)),
+    ], scale=1.5, mult=0.9, loop=(0, 2, 2))
+    folder = fh.write_model(tmp_path / "long", raw, 61)
+    gen = torch.Generator().manual_seed(8)
+    requests = {"r0": torch.randint(0, 131, (400,), generator=gen).tolist()}
+    config, tensors = fh.read_model(folder)
+    oracle = {"r0": plain.forward(config, tensors, requests["r0"]).float()}
+    whole = _check(folder, dtype, helpers.trace_whole(requests), requests, oracle, 16)
+    tail = _check(folder, dtype, helpers.trace_tail(requests, tail=160), requests, oracle, 16)
+    chunks = _check(folder, dtype, helpers.trace_chunks(requests, 4), requests, oracle, 16, fragment=9)
+    cut = (2e-5 if dtype == torch.float32 else 2.0 ** -6) * max(1.0, float(oracle["r0"].abs().max()))
+    for other in (tail, chunks):
+        assert float((other["r0"] - whole["r0"]).abs().max()) <= cut
+
+
 WINDOWS = (24, 19)          # of the attention layer and of the latent layer below
 
 
